@@ -12,6 +12,7 @@ from pathlib import Path
 from typing import Any, Callable, Dict, Mapping
 
 from .kabanex import ARCHITECTURE as KABANEX, KabanexConfig
+from .kivezen import ARCHITECTURE as KIVEZEN, KivezenConfig
 from .llama import ConfigError, LlamaConfig
 from .lovurax import ARCHITECTURE as LOVURAX, LovuraxConfig
 
@@ -66,3 +67,4 @@ def load_config(folder):
 register_architecture("LlamaForCausalLM", LlamaConfig.from_dict)
 register_architecture(KABANEX, KabanexConfig.from_dict)
 register_architecture(LOVURAX, LovuraxConfig.from_dict)
+register_architecture(KIVEZEN, KivezenConfig.from_dict)

@@ -19,13 +19,18 @@ from typing import Mapping, Optional, Tuple
 
 @dataclass(frozen=True)
 class RopeScalingSpec:
-    """How pair frequencies are stretched.  kind: "linear" (angle * 1/factor) or "llama3"."""
+    """How pair frequencies are stretched.  kind: "linear" (angle * 1/factor), "llama3", or "yarn": with
+    pair(t) = dims * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(pair(high_freq_factor)), 0) and
+    hi = min(ceil(pair(low_freq_factor)), dims - 1), pair i has ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) and
+    the frequency f_i / factor * ramp_i + f_i * (1 - ramp_i): pairs that turn often within `original` positions keep
+    their frequency, slow ones are divided by `factor`."""
 
     kind: str
     factor: float
     low_freq_factor: float = 0.0
     high_freq_factor: float = 0.0
     original_max_position: int = 0
+    magnitude: float = 1.0  # multiplies every cosine and sine of the table
 
 
 @dataclass(frozen=True)
@@ -226,6 +231,9 @@ class ModelSpec:
     head: HeadSpec
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    # Copies of the residual stream that the blocks keep side by side ([tokens, streams * width]); they all start as
+    # the embedding's rows and are added up before the final norm.  1: the usual single stream.
+    residual_streams: int = 1
     # Tensors a checkpoint of this architecture may hold that the model does not read: name patterns
     # (fnmatch) of buffers that are recomputed, and names that must repeat another tensor exactly (a
     # tied model's stored output matrix).  Anything else that is not asked for is an error.
@@ -310,6 +318,12 @@ class RetentionSpec:
     position: Optional[RopeSpec]
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
     kind: str = "retention"
+    # Variations.  `input_activation` (a name of the activation table, or None) is applied to q, k and v as they leave
+    # their products.  `norm` "head": every head's o_t is divided by its own root mean square, no gain; "all": the heads
+    # side by side pass ONE RMS norm with a gain tensor (`weights["norm"]`).  `gate_activation`: "silu" or "sigmoid".
+    input_activation: Optional[str] = None
+    norm: str = "head"
+    gate_activation: str = "silu"
 
 
 @dataclass(frozen=True)
@@ -325,3 +339,74 @@ class GatedResidualBlockSpec:
     feed_forward_norm: Optional[object]
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
     kind: str = "prenorm_gated"
+
+
+@dataclass(frozen=True)
+class CappedAttentionSpec:
+    """Causal grouped-query softmax attention with a bounded score and an optional sink.
+    q and k are rotated (`position`, or None) and then, with `unit_norm`, divided by their root mean square per head
+    (eps `eps`, no gain).  score = scale * temperature_h * q.k with one learned number per head (`head_temperature`,
+    `weights["temperature"]`; else 1), then with `softcap` c != 0: c * tanh(score / c).  `sink`: the softmax has one more
+    term of score 0 in its denominator that has no value, p_j = exp(s_j) / (1 + sum exp(s_j)).
+    `value_position`: the value of position j is rotated by j over its first `rotary_dim` coordinates before it is
+    cached, and every head's result at position i is rotated back by -i after the sum over the keys."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    position: Optional[RopeSpec]
+    unit_norm: bool
+    value_position: Optional[RopeSpec]
+    head_temperature: bool
+    softcap: float
+    sink: bool
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "capped_attention"
+
+
+@dataclass(frozen=True)
+class ClampedExpertSpec:
+    """One gated feed-forward with clamped branches: g = min(gate . x, limit), u = clamp(up . x, -limit, limit),
+    down . (g * sigmoid(swish_slope * g) * (u + 1)); no biases."""
+
+    intermediate_size: int
+    limit: float
+    swish_slope: float
+
+
+@dataclass(frozen=True)
+class RoutedFeedForwardSpec:
+    """A mixture of `num_experts` feed-forwards of one shape (`expert`): router logits z = router . x in float32; every
+    token uses the `top` experts with the largest logits (ties to the lower index) with the softmax over the chosen
+    logits as weights.  `shared`: one more expert that every token uses, multiplied by sigmoid(shared_gate . x), one
+    number per token.  `weights`: router, shared_gate, shared_{gate,up,down}, and expert_{gate,up,down} with `{expert}`
+    in the name."""
+
+    hidden_size: int
+    num_experts: int
+    top: int
+    expert: ClampedExpertSpec
+    shared: Optional[ClampedExpertSpec]
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "routed"
+
+
+@dataclass(frozen=True)
+class HyperBlockSpec:
+    """A pre-norm layer over `streams` copies of the residual stream (hyper-connections).  For the mixer and then, if
+    the layer has one, the feed-forward: u = sum_s in[s] x_s; y = sublayer(norm(u)); then all copies at once from the old
+    ones, x_t <- sum_s mix[s, t] x_s + out[t] y.  in, out [streams] and mix [streams, streams] are tensors
+    (`weights`: mixer_in, mixer_out, mixer_mix, feed_forward_in, ...).  `streams` 0: one stream and no such tensors,
+    x <- x + sublayer(norm(x))."""
+
+    mixer: object
+    feed_forward: Optional[object]
+    mixer_norm: object
+    feed_forward_norm: Optional[object]
+    streams: int
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "prenorm_hyper"

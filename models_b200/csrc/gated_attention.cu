@@ -7,6 +7,11 @@
 //   out_h(i) = gate * sum_j weight(i, j) v_c(j)
 //   gate: none, sigmoid of one number per (token, head), or sigmoid of one number per output element
 //
+// Variations of the score (ScoreExtras): a learned factor per head on the scaled product (scale * factor_h * q.k); a
+// bound, score <- cap * tanh(score / cap), applied after everything else; a sink, one more term of score 0 that has no
+// value in the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)); and values that were stored rotated by their
+// own position (pairs 2m, 2m + 1): the head's sum is then turned back by the query's position before any gate.
+//
 // Keys have head_dim coordinates and values value_dim; the value rows may lie in a pool of their own or be the
 // first value_dim coordinates of the key rows (a cache that keeps one row per position, read as key and as value).
 //
@@ -26,12 +31,108 @@ namespace mb {
 
 constexpr int kGateHead = 1, kGateElement = 2;  // gate kinds (0: no gate)
 
+struct ScoreExtras {
+    const float* head_scale;  // [heads] factors on the scaled product, or null
+    float softcap;            // 0: scores are not bounded
+    int sink;                 // != 0: the softmax's denominator has one more term of score 0
+    const float* turn_cos;    // [positions][value_dim / 2] with turn_sin: the result's pairs (2m, 2m + 1) are turned by
+    const float* turn_sin;    // minus the query's position; null: the result stays as it is
+};
+
+__device__ __forceinline__ float bounded(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
+
+// (x, y) of a pair turned by minus the angle whose cosine and sine are c and s.
+__device__ __forceinline__ float turned_back(float mine, float partner, bool first_of_pair, float c, float s) {
+    return first_of_pair ? mine * c + partner * s : mine * c - partner * s;
+}
+
 __device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 // grid (tokens); block: a multiple of 32 threads; a warp per head.
 //   q head (in place): q / rms(q) * q_gain * (1 + temp_coef * ln(floor((p + 1) / temp_every) + 1))
 //   k head (into the cache): k / rms(k) * k_gain;  v head (into the cache, if value_dim > 0): as it is.
 // rms(x) = sqrt(mean(x^2) + eps).  A null gain means: that side is not normalised.
+//
+// With a Rotation, query and key heads are first rotated by the token's position over their first `dim` coordinates
+// (tables [positions][dim / 2]; pairs (i, i + dim / 2), or (2i, 2i + 1) when `interleaved`), and with `unit` they are then
+// divided by their root mean square without any gain; value heads are rotated over their first `value_dim_rotated`
+// coordinates by tables of their own on their way into the cache.  Heads of up to 256 coordinates.
+struct Rotation {
+    const float* cos;
+    const float* sin;
+    int dim;
+    int interleaved;
+    int unit;
+    const float* value_cos;
+    const float* value_sin;
+    int value_dim_rotated;
+};
+
+// coordinate d of a head rotated by the angle of table row `at` ([dim / 2] cosines and sines)
+template <typename T>
+__device__ __forceinline__ float rotated_coordinate(const T* __restrict__ src, int d, int dim, int interleaved,
+                                                    const float* __restrict__ cos_row, const float* __restrict__ sin_row) {
+    const float x = Num<T>::load(src + d);
+    if (d >= dim) return x;
+    const int half = dim / 2;
+    const bool first = interleaved ? (d & 1) == 0 : d < half;
+    const int pair = interleaved ? d >> 1 : (d < half ? d : d - half);
+    const int other = interleaved ? d ^ 1 : (d < half ? d + half : d - half);
+    const float partner = Num<T>::load(src + other);
+    return first ? x * cos_row[pair] - partner * sin_row[pair] : x * cos_row[pair] + partner * sin_row[pair];
+}
+
+template <typename T>
+__global__ void rotate_norm_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                                         const T* __restrict__ v, int v_stride, const int* __restrict__ positions, float eps,
+                                         Rotation rotation, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                         const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
+                                         int value_dim, int page_size) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    constexpr int kPer = 8;
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int pos = positions[token];
+    const int slot = slot_mapping[token];
+    const size_t page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+    const float* cos_row = rotation.dim > 0 ? rotation.cos + (size_t)pos * (rotation.dim / 2) : nullptr;
+    const float* sin_row = rotation.dim > 0 ? rotation.sin + (size_t)pos * (rotation.dim / 2) : nullptr;
+    for (int item = warp; item < heads + kv_heads; item += warps) {
+        const bool is_query = item < heads;
+        const int head = is_query ? item : item - heads;
+        if (!is_query && slot < 0) continue;  // a padding row stores nothing
+        T* q_head = q + (size_t)token * q_stride + (size_t)head * head_dim;
+        const T* src = is_query ? q_head : k + (size_t)token * k_stride + (size_t)head * head_dim;
+        T* dst = is_query ? q_head : k_pool + ((page * kv_heads + head) * page_size + offset) * head_dim;
+        float value[kPer];
+        float ssq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int d = lane + 32 * i;
+            value[i] = d < head_dim ? rotated_coordinate<T>(src, d, rotation.dim, rotation.interleaved, cos_row, sin_row) : 0.0f;
+            ssq = fmaf(value[i], value[i], ssq);
+        }
+        __syncwarp();  // a query head is rewritten in place: every lane has read its partners
+        const float factor = rotation.unit ? 1.0f / sqrtf(warp_sum(ssq) / (float)head_dim + eps) : 1.0f;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) Num<T>::store(dst + d, value[i] * factor);
+        }
+    }
+    if (slot < 0 || value_dim <= 0) return;
+    const T* v_row = v + (size_t)token * v_stride;
+    const int turned = rotation.value_dim_rotated;
+    const float* value_cos = turned > 0 ? rotation.value_cos + (size_t)pos * (turned / 2) : nullptr;
+    const float* value_sin = turned > 0 ? rotation.value_sin + (size_t)pos * (turned / 2) : nullptr;
+    for (int item = threadIdx.x; item < kv_heads * value_dim; item += blockDim.x) {
+        const int head = item / value_dim, d = item % value_dim;
+        const float x = rotated_coordinate<T>(v_row + (size_t)head * value_dim, d, turned, rotation.interleaved, value_cos, value_sin);
+        Num<T>::store(v_pool + ((page * kv_heads + head) * page_size + offset) * value_dim + d, x);
+    }
+}
+
 template <typename T>
 __global__ void norm_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
                                   const T* __restrict__ v, int v_stride, const int* __restrict__ positions,
@@ -107,7 +208,7 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                             const int* __restrict__ kv_lens, const float* __restrict__ head_bias,
                             const T* __restrict__ gate, int gate_stride, int gate_kind, int heads, int kv_heads,
-                            int head_dim, int value_dim, int page_size, float scale, float slope_exponent) {
+                            int head_dim, int value_dim, int page_size, float scale, float slope_exponent, ScoreExtras extras) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ float q_shared_all[];  // kWarps * head_dim floats
@@ -123,6 +224,7 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
     const float slope = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head + 1) / (float)heads) : 0.0f;
     const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
+    if (extras.head_scale != nullptr) scale *= extras.head_scale[head];
 
     float* q_shared = q_shared_all + warp * head_dim;
     const T* q_row = q + (size_t)row * q_stride + (size_t)head * head_dim;
@@ -132,7 +234,8 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float acc[kAcc];
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) acc[i] = 0.0f;
-    float running_max = -CUDART_INF_F, running_sum = 0.0f;
+    // (a sink is a key of score 0 whose value is zero: it is there before the first chunk)
+    float running_max = kSoftmax && extras.sink ? 0.0f : -CUDART_INF_F, running_sum = kSoftmax && extras.sink ? 1.0f : 0.0f;
     const int* table = block_table + (size_t)seq * max_blocks;
 
     for (int chunk = 0; chunk <= pos; chunk += 32) {
@@ -143,7 +246,8 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
         const bool visible = p <= pos;
         float score = -CUDART_INF_F;
         if (visible)
-            score = dot_row<T>(q_shared, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale - slope * (float)(pos - p) + bias;
+            score = bounded(dot_row<T>(q_shared, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale - slope * (float)(pos - p) + bias,
+                            extras.softcap);
         float weight;
         if (kSoftmax) {
             const float new_max = fmaxf(running_max, warp_max(score));  // finite: every chunk holds a visible key
@@ -170,6 +274,15 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float factor = kSoftmax ? 1.0f / running_sum : 1.0f;
     if (gate_kind == kGateHead) factor *= sigmoid(Num<T>::load(gate + (size_t)row * gate_stride + head));
     T* out_row = out + (size_t)row * out_stride + (size_t)head * value_dim;
+    if (extras.turn_cos != nullptr) {  // (every lane takes part in the exchange; value_dim is even, so a pair is whole)
+        const size_t at = (size_t)pos * (value_dim / 2);
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) {
+            const int d = lane + 32 * i;
+            const float partner = __shfl_xor_sync(0xffffffffu, acc[i], 1);
+            if (d < value_dim) acc[i] = turned_back(acc[i], partner, (d & 1) == 0, extras.turn_cos[at + d / 2], extras.turn_sin[at + d / 2]);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) {
         const int d = lane + 32 * i;
@@ -200,7 +313,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
                               int v_width, const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                               const int* __restrict__ kv_lens, const float* __restrict__ head_bias, float* __restrict__ partial,
                               int span, int heads, int kv_heads, int head_dim, int value_dim, int page_size, float scale,
-                              float slope_exponent, int staged) {
+                              float slope_exponent, int staged, ScoreExtras extras) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float decode_shared[];
@@ -236,11 +349,12 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
     for (int i = threadIdx.x; i < count * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
     __syncthreads();
     const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
-    float slope[kGroup], bias[kGroup], run_max[kGroup], run_sum[kGroup], acc[kGroup][kAcc];
+    float slope[kGroup], bias[kGroup], factor_of[kGroup], run_max[kGroup], run_sum[kGroup], acc[kGroup][kAcc];
 #pragma unroll
     for (int g = 0; g < kGroup; ++g) {
         slope[g] = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head0 + g + 1) / (float)heads) : 0.0f;
         bias[g] = (head_bias != nullptr && g < count) ? head_bias[head0 + g] : 0.0f;
+        factor_of[g] = (extras.head_scale != nullptr && g < count) ? scale * extras.head_scale[head0 + g] : scale;
         run_max[g] = -CUDART_INF_F;
         run_sum[g] = 0.0f;
 #pragma unroll
@@ -306,7 +420,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         float weight[kGroup];
 #pragma unroll
         for (int g = 0; g < kGroup; ++g) {
-            const float z = visible ? score[g] * scale - slope[g] * (float)(pos - p) + bias[g] : -CUDART_INF_F;
+            const float z = visible ? bounded(score[g] * factor_of[g] - slope[g] * (float)(pos - p) + bias[g], extras.softcap) : -CUDART_INF_F;
             if (kSoftmax) {
                 const float new_max = fmaxf(run_max[g], warp_max(z));  // finite: the chunk holds a visible key
                 weight[g] = visible ? expf(z - new_max) : 0.0f;
@@ -383,17 +497,20 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
 template <typename T, bool kSoftmax>
 __global__ void gated_attention_combine_kernel(const float* __restrict__ partial, int splits, T* __restrict__ out, int out_stride,
                                                const int* __restrict__ cu_q, const T* __restrict__ gate, int gate_stride,
-                                               int gate_kind, int heads, int value_dim) {
+                                               int gate_kind, int heads, int value_dim, const int* __restrict__ kv_lens,
+                                               ScoreExtras extras) {
     grid_launch_dependents();
     grid_dependency_wait();
-    const int head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    if (d >= value_dim) return;
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const bool live = (int)threadIdx.x < value_dim;
+    const int d = live ? threadIdx.x : 0;  // (a thread beyond the values follows along for the exchange below and stores nothing)
     const int stride = 2 + value_dim;
     const float* mine = partial + ((size_t)seq * heads + head) * splits * stride;
-    float top = -CUDART_INF_F;
+    const bool sink = kSoftmax && extras.sink;
+    float top = sink ? 0.0f : -CUDART_INF_F;
     if (kSoftmax)
         for (int s = 0; s < splits; ++s) top = fmaxf(top, mine[(size_t)s * stride]);
-    float sum = 0.0f, weights = 0.0f;
+    float sum = 0.0f, weights = sink ? expf(-top) : 0.0f;
     for (int s = 0; s < splits; ++s) {
         const float* run = mine + (size_t)s * stride;
         if (run[1] == 0.0f) continue;  // a run beyond the sequence's end
@@ -402,6 +519,12 @@ __global__ void gated_attention_combine_kernel(const float* __restrict__ partial
         weights = fmaf(run[1], factor, weights);
     }
     float value = kSoftmax ? sum / weights : sum;
+    if (extras.turn_cos != nullptr) {
+        const size_t at = (size_t)(kv_lens[seq] - 1) * (value_dim / 2) + d / 2;
+        const float partner = __shfl_xor_sync(0xffffffffu, value, 1);
+        value = turned_back(value, partner, (d & 1) == 0, extras.turn_cos[at], extras.turn_sin[at]);
+    }
+    if (!live) return;
     const size_t row = cu_q[seq];
     if (gate_kind == kGateHead) value *= sigmoid(Num<T>::load(gate + row * gate_stride + head));
     if (gate_kind == kGateElement) value *= sigmoid(Num<T>::load(gate + row * gate_stride + (size_t)head * value_dim + d));
@@ -577,18 +700,29 @@ int launch_norm_store(void* q, int q_stride, const void* k, int k_stride, const 
     return 0;
 }
 
+template <typename T>
+int launch_rotate_norm_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const int* positions,
+                             float eps, Rotation rotation, void* k_pool, void* v_pool, const int* slot_mapping, int tokens, int heads,
+                             int kv_heads, int head_dim, int value_dim, int page_size, cudaStream_t stream) {
+    const int warps = heads + kv_heads < 4 ? 4 : (heads + kv_heads > 16 ? 16 : heads + kv_heads);
+    MB_LAUNCH("rotate_norm_store", rotate_norm_store_kernel<T>, dim3(tokens), dim3(32 * warps), 0, stream, true, (T*)q, q_stride,
+              (const T*)k, k_stride, (const T*)v, v_stride, positions, eps, rotation, (T*)k_pool, (T*)v_pool, slot_mapping, heads,
+              kv_heads, head_dim, value_dim, page_size);
+    return 0;
+}
+
 template <typename T, int kAcc, bool kSoftmax>
 int launch_rows(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool, int v_width,
                 const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens, const float* head_bias,
                 const void* gate, int gate_stride, int gate_kind, int sequences, int max_q_len, int heads, int kv_heads,
-                int head_dim, int value_dim, int page_size, float scale, float slope_exponent, cudaStream_t stream) {
+                int head_dim, int value_dim, int page_size, float scale, float slope_exponent, ScoreExtras extras, cudaStream_t stream) {
     constexpr int kWarps = 4;
     const dim3 grid((max_q_len + kWarps - 1) / kWarps, heads, sequences);
     const size_t smem = (size_t)kWarps * head_dim * sizeof(float);
     MB_LAUNCH("gated_attention_rows", (gated_attention_rows_kernel<T, kWarps, kAcc, kSoftmax>), dim3(grid), dim3(kWarps * 32), smem,
               stream, true, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, v_width, block_table,
               max_blocks, cu_q, kv_lens, head_bias, (const T*)gate, gate_stride, gate_kind, heads, kv_heads, head_dim, value_dim,
-              page_size, scale, slope_exponent);
+              page_size, scale, slope_exponent, extras);
     return 0;
 }
 
@@ -624,14 +758,48 @@ MB_EXPORT int mb_norm_store(void* q, int q_stride, const void* k, int k_stride, 
     return status ? status : check_launch("norm_store");
 }
 
+// Query heads (in place) and key heads (into the cache) rotated by the token's position over their first rotary_dim
+// coordinates and then, with unit != 0, divided by their root mean square; value heads rotated over their first
+// value_rotary_dim coordinates by tables of their own and stored.  Tables [positions][dim / 2] floats.
+MB_EXPORT int mb_rotate_norm_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                                   const int* positions, const float* cos_table, const float* sin_table, int rotary_dim,
+                                   int interleaved, int unit, float eps, const float* value_cos, const float* value_sin,
+                                   int value_rotary_dim, void* k_pool, void* v_pool, const int* slot_mapping, int tokens, int heads,
+                                   int kv_heads, int head_dim, int value_dim, int page_size, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 256 || kv_heads <= 0 || heads < 0 || value_dim < 0 || page_size <= 0)
+        return fail("rotate_norm_store: heads %d, kv heads %d, head_dim %d (at most 256), value_dim %d", heads, kv_heads, head_dim, value_dim);
+    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim || (rotary_dim > 0 && (cos_table == nullptr || sin_table == nullptr)))
+        return fail("rotate_norm_store: rotary_dim %d must be even, at most %d, and come with its tables", rotary_dim, head_dim);
+    if (value_rotary_dim < 0 || value_rotary_dim % 2 || value_rotary_dim > value_dim ||
+        (value_rotary_dim > 0 && (value_cos == nullptr || value_sin == nullptr)))
+        return fail("rotate_norm_store: value_rotary_dim %d must be even, at most %d, and come with its tables", value_rotary_dim, value_dim);
+    const Rotation rotation{cos_table, sin_table, rotary_dim, interleaved, unit, value_cos, value_sin, value_rotary_dim};
+    int status;
+    if (dtype == MB_F32)
+        status = launch_rotate_norm_store<float>(q, q_stride, k, k_stride, v, v_stride, positions, eps, rotation, k_pool, v_pool,
+                                                 slot_mapping, tokens, heads, kv_heads, head_dim, value_dim, page_size, stream);
+    else if (dtype == MB_BF16)
+        status = launch_rotate_norm_store<__nv_bfloat16>(q, q_stride, k, k_stride, v, v_stride, positions, eps, rotation, k_pool, v_pool,
+                                                         slot_mapping, tokens, heads, kv_heads, head_dim, value_dim, page_size, stream);
+    else
+        return fail("rotate_norm_store: unknown dtype code %d", dtype);
+    return status ? status : check_launch("rotate_norm_store");
+}
+
 // q: rows of `heads` heads of head_dim (row stride in elements); out: rows of `heads` heads of value_dim.
 // softmax != 0: softmax weights; 0: sigmoid weights.  gate_kind: 0 none, 1 [tokens, heads], 2 [tokens, heads * value_dim].
 MB_EXPORT int mb_gated_attention_rows(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
                                       const void* v_pool, int v_width, const int* block_table, int max_blocks, const int* cu_q,
                                       const int* kv_lens, const float* head_bias, const void* gate, int gate_stride, int gate_kind,
                                       int sequences, int max_q_len, int heads, int kv_heads, int head_dim, int value_dim,
-                                      int page_size, int softmax, float scale, float slope_exponent, cudaStream_t stream) {
+                                      int page_size, int softmax, float scale, float slope_exponent, const float* head_scale,
+                                      float softcap, int sink, const float* turn_cos, const float* turn_sin, cudaStream_t stream) {
     if (sequences <= 0 || max_q_len <= 0) return 0;
+    if ((turn_cos == nullptr) != (turn_sin == nullptr) || (turn_cos != nullptr && value_dim % 2))
+        return fail("gated_attention_rows: turning the result back needs both tables and an even value_dim (%d)", value_dim);
+    if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_rows: softcap %g, a sink without a softmax", softcap);
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
     if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_rows: head_dim %d is outside 1..2048", head_dim);
     if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
         return fail("gated_attention_rows: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
@@ -643,7 +811,7 @@ MB_EXPORT int mb_gated_attention_rows(const void* q, int q_stride, void* out, in
 #define MB_ROWS(T, S)                                                                                                          \
     pick_rows<T, S>(value_dim, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table, max_blocks, cu_q, kv_lens,  \
                     head_bias, gate, gate_stride, gate_kind, sequences, max_q_len, heads, kv_heads, head_dim, value_dim,       \
-                    page_size, scale, slope_exponent, stream)
+                    page_size, scale, slope_exponent, extras, stream)
     if (dtype == MB_F32)
         status = softmax ? MB_ROWS(float, true) : MB_ROWS(float, false);
     else if (dtype == MB_BF16)
@@ -661,7 +829,7 @@ int launch_decode(const void* q, int q_stride, void* out, int out_stride, const 
                   const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens, const float* head_bias,
                   const void* gate, int gate_stride, int gate_kind, int sequences, int heads, int kv_heads, int head_dim,
                   int value_dim, int page_size, float scale, float slope_exponent, int splits, int span, float* partial,
-                  cudaStream_t stream) {
+                  ScoreExtras extras, cudaStream_t stream) {
     const int group = heads / kv_heads, parts = (group + kGroup - 1) / kGroup;
     size_t smem = ((size_t)kGroup * head_dim + 4 * (size_t)kGroup * (2 + value_dim)) * sizeof(float);
     // a chunk per warp in shared memory where rows are whole 16-byte pieces and four chunks fit beside the rest
@@ -677,10 +845,10 @@ int launch_decode(const void* q, int q_stride, void* out, int out_stride, const 
     }
     MB_LAUNCH("gated_attention_decode", kernel, dim3(splits, kv_heads * parts, sequences), dim3(128), smem, stream, true, (const T*)q,
               q_stride, (const T*)k_pool, (const T*)v_pool, v_width, block_table, max_blocks, cu_q, kv_lens, head_bias, partial, span,
-              heads, kv_heads, head_dim, value_dim, page_size, scale, slope_exponent, staged ? 1 : 0);
+              heads, kv_heads, head_dim, value_dim, page_size, scale, slope_exponent, staged ? 1 : 0, extras);
     MB_LAUNCH("gated_attention_combine", (gated_attention_combine_kernel<T, kSoftmax>), dim3(heads, sequences),
               dim3((value_dim + 31) / 32 * 32), 0, stream, true, (const float*)partial, splits, (T*)out, out_stride, cu_q,
-              (const T*)gate, gate_stride, gate_kind, heads, value_dim);
+              (const T*)gate, gate_stride, gate_kind, heads, value_dim, kv_lens, extras);
     return 0;
 }
 
@@ -708,8 +876,13 @@ MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, 
                                         const int* kv_lens, const float* head_bias, const void* gate, int gate_stride, int gate_kind,
                                         int sequences, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
                                         int softmax, float scale, float slope_exponent, int splits, int span, float* partial,
-                                        cudaStream_t stream) {
+                                        const float* head_scale, float softcap, int sink, const float* turn_cos,
+                                        const float* turn_sin, cudaStream_t stream) {
     if (sequences <= 0) return 0;
+    if ((turn_cos == nullptr) != (turn_sin == nullptr) || (turn_cos != nullptr && value_dim % 2))
+        return fail("gated_attention_decode: turning the result back needs both tables and an even value_dim (%d)", value_dim);
+    if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_decode: softcap %g, a sink without a softmax", softcap);
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
     if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_decode: head_dim %d is outside 1..2048", head_dim);
     if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
         return fail("gated_attention_decode: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
@@ -724,7 +897,7 @@ MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, 
 #define MB_DECODE(T, S)                                                                                                          \
     mb::pick_decode<T, S>(heads / kv_heads, value_dim, many_blocks, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table,       \
                           max_blocks, cu_q, kv_lens, head_bias, gate, gate_stride, gate_kind, sequences, heads, kv_heads, head_dim, \
-                          value_dim, page_size, scale, slope_exponent, splits, span, partial, stream)
+                          value_dim, page_size, scale, slope_exponent, splits, span, partial, extras, stream)
     if (dtype == MB_F32)
         status = softmax ? MB_DECODE(float, true) : MB_DECODE(float, false);
     else if (dtype == MB_BF16)

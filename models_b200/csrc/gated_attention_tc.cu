@@ -5,6 +5,9 @@
 //   score(i, j) = scale * q_h(i) . k_c(j) - slope_h * (i - j) + bias_h,   weight: softmax over j <= i, or sigmoid
 //   out_h(i) = gate * sum_j weight(i, j) v_c(j)
 //
+// and the same variations of the score as there (ScoreExtras: a factor per head, a bound cap * tanh(. / cap), a sink in
+// the softmax's denominator, a result whose pairs (2m, 2m + 1) are turned back by the query's position).
+//
 // A block owns 64 query tokens of one head (a warp 16 of them) and walks the pages of keys up to its last token
 // through two stages of cp.async copies.  Scores are m16n8k16 products with float accumulators; slope, bias, mask,
 // sigmoid or running softmax are float arithmetic on them.  The weights stay float: a tensor-core operand is bfloat16,
@@ -42,6 +45,14 @@ constexpr bool kKeepQueries = KD <= 128;  // query fragments in registers; beyon
 constexpr int kGateHead = 1, kGateElement = 2;
 
 using bf16 = __nv_bfloat16;
+
+struct ScoreExtras {
+    const float* head_scale;  // [heads] factors on the scaled product, or null
+    float softcap;            // 0: scores are not bounded
+    int sink;                 // != 0: the softmax's denominator has one more term of score 0
+    const float* turn_cos;    // [positions][VD / 2] with turn_sin: the result's pairs are turned by minus the query's position
+    const float* turn_sin;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -117,7 +128,7 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
                           const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
                           int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                           const float* __restrict__ head_bias, const bf16* __restrict__ gate, int gate_stride, int gate_kind,
-                          int heads, int kv_heads, float scale, float slope_exponent) {
+                          int heads, int kv_heads, float scale, float slope_exponent, ScoreExtras extras) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -139,6 +150,9 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
     const float slope = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head + 1) / (float)heads) : 0.0f;
     const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
     constexpr float kLog2e = 1.4426950408889634f;
+    if (extras.head_scale != nullptr) scale *= extras.head_scale[head];
+    const float cap = extras.softcap;
+    const float cap_exponent = cap > 0.0f ? 2.0f * kLog2e / cap : 0.0f;
 
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
@@ -166,6 +180,10 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
 #pragma unroll
     for (int i = 0; i < VD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    if (kSoftmax && extras.sink) {  // a key of score 0 whose value is zero, there before the first tile; one lane of four counts it
+        run_max[0] = run_max[1] = 0.0f;
+        run_sum[0] = run_sum[1] = tid4 == 0 ? 1.0f : 0.0f;
+    }
     int row_pos[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -225,6 +243,8 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
                     const int key = key_base + nt * 8 + tid4 * 2 + (i & 1);
                     const int r = i >> 1;
                     float z = fmaf(s[nt][i], scale, bias) - slope * (float)(row_pos[r] - key);
+                    // cap * tanh(z / cap) with tanh(x) = 1 - 2 / (1 + e^(2x))
+                    if (cap > 0.0f) z = cap - __fdividef(2.0f * cap, 1.0f + fast_exp2(z * cap_exponent));
                     if (!full && key > row_pos[r]) z = -CUDART_INF_F;
                     if (kSoftmax) {
                         part_max[r] = fmaxf(part_max[r], z);
@@ -287,10 +307,17 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
         float factor = kSoftmax ? 1.0f / total : 1.0f;
         if (gate_kind == kGateHead) factor *= 1.0f / (1.0f + expf(-__bfloat162float(gate[token * gate_stride + head])));
         bf16* out_row = out + token * out_stride + (size_t)head * VD;
+        const size_t turn_at = extras.turn_cos != nullptr ? (size_t)row_pos[r] * (VD / 2) : 0;
 #pragma unroll
         for (int i = 0; i < VD / 8; ++i) {
             const int d = i * 8 + tid4 * 2;
             float x = o[i][2 * r] * factor, y = o[i][2 * r + 1] * factor;
+            if (extras.turn_cos != nullptr) {
+                const float c = extras.turn_cos[turn_at + d / 2], sn = extras.turn_sin[turn_at + d / 2];
+                const float x0 = x;
+                x = x0 * c + y * sn;
+                y = y * c - x0 * sn;
+            }
             if (gate_kind == kGateElement) {
                 const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + token * gate_stride + (size_t)head * VD + d));
                 x *= 1.0f / (1.0f + expf(-g.x));
@@ -316,8 +343,12 @@ MB_EXPORT int mb_gated_attention_tc(const void* q, int q_stride, void* out, int 
                                     const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens,
                                     const float* head_bias, const void* gate, int gate_stride, int gate_kind, int sequences,
                                     int max_q_len, int heads, int kv_heads, int page_size, int softmax, float scale,
-                                    float slope_exponent, cudaStream_t stream) {
+                                    float slope_exponent, const float* head_scale, float softcap, int sink, const float* turn_cos,
+                                    const float* turn_sin, cudaStream_t stream) {
     if (sequences <= 0 || max_q_len <= 0) return 0;
+    if ((turn_cos == nullptr) != (turn_sin == nullptr)) return fail("gated_attention_tc: turning the result back needs both tables");
+    if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_tc: softcap %g, a sink without a softmax", softcap);
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
     if (page_size != kTile) return fail("gated_attention_tc: cache pages must hold %d positions, got %d", kTile, page_size);
     if (kv_heads <= 0 || heads % kv_heads) return fail("gated_attention_tc: %d heads are no multiple of %d kv heads", heads, kv_heads);
     if (sequences > 65535 || heads > 65535) return fail("gated_attention_tc: %d sequences or %d heads exceed the grid limit 65535", sequences, heads);
@@ -336,10 +367,10 @@ MB_EXPORT int mb_gated_attention_tc(const void* q, int q_stride, void* out, int 
     if (softmax)
         MB_LAUNCH("gated_attention_tc", gated_attention_tc_kernel<true>, dim3(grid), dim3(kThreads), kSmemBytes, stream, true, (const bf16*)q,
                   q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_q, kv_lens, head_bias,
-                  (const bf16*)gate, gate_stride, gate_kind, heads, kv_heads, scale, slope_exponent);
+                  (const bf16*)gate, gate_stride, gate_kind, heads, kv_heads, scale, slope_exponent, extras);
     else
         MB_LAUNCH("gated_attention_tc", gated_attention_tc_kernel<false>, dim3(grid), dim3(kThreads), kSmemBytes, stream, true, (const bf16*)q,
                   q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_q, kv_lens, head_bias,
-                  (const bf16*)gate, gate_stride, gate_kind, heads, kv_heads, scale, slope_exponent);
+                  (const bf16*)gate, gate_stride, gate_kind, heads, kv_heads, scale, slope_exponent, extras);
     return check_launch("gated_attention_tc");
 }

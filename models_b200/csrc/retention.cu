@@ -7,6 +7,10 @@
 //   o_t = S_t^T q_t
 //   y_t = out_scale * o_t / sqrt(mean(o_t^2) + eps) * silu(g_t)          (the mean over the head's value_dim numbers)
 //
+// Variations: `input_act` >= 0 applies that activation of the activation table to q, k and v as they are read (before
+// any rotation); with `raw_out` the kernel stops after o_t and writes out_scale * o_t as floats (no norm, no gate): what
+// comes after it is then another kernel's, for instance one norm over all heads (group_norm_gate below).
+//
 // q, k, v, g are projections of the token (storage type, float or bfloat16); everything after them is float.
 //
 // A block owns one (sequence, head): a thread per value coordinate j keeps column j of S in shared memory
@@ -48,7 +52,8 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                       const float* __restrict__ sin_table, int rotary_dim, const float* __restrict__ decay, float key_scale,
                       float eps, float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
                       int heads, int head_dim, int value_dim, T* __restrict__ out, int out_stride, float out_scale,
-                      int run_length, float* __restrict__ scratch, int async_ok) {
+                      int run_length, float* __restrict__ scratch, int async_ok, int input_act, float* __restrict__ raw_out,
+                      int raw_stride) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float shared[];
@@ -73,6 +78,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const bool live = j < value_dim;
     const int half = rotary_dim / 2;
     const float a = decay[head];
+    const bool no_gate = kMode == kSummarise || raw_out != nullptr;
     float* stored = kMode == kWhole ? state + ((size_t)slots[seq] * heads + head) * head_dim * value_dim
                                     : scratch + (((size_t)seq * heads + head) * gridDim.z + run) * head_dim * value_dim;
     if (kDim > 0) {
@@ -92,8 +98,9 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             const bool is_qk = c < 2 * head_dim;
             const bool is_key = is_qk && c >= head_dim;
             const bool is_gate = !is_qk && c >= 2 * head_dim + value_dim;
-            if (kMode == kSummarise && ((is_qk && !is_key) || is_gate)) continue;  // no results: no queries, no gates
+            if ((kMode == kSummarise && is_qk && !is_key) || (no_gate && is_gate)) continue;  // no results: no queries, no gates
             const int d = is_qk ? (is_key ? c - head_dim : c) : c - 2 * head_dim - (is_gate ? value_dim : 0);
+            const bool activated = input_act >= 0 && !is_gate;
             const T* source = (is_qk ? (is_key ? k : q) + (size_t)head * head_dim : (is_gate ? g : v) + (size_t)head * value_dim)
                               + (size_t)(first + t0) * in_stride;
             const bool rotated = is_qk && d < rotary_dim;
@@ -107,9 +114,12 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                 if (u < n) {
                     const T* x = source + (size_t)u * in_stride;
                     value[u] = Num<T>::load(x + d);
+                    if (activated) value[u] = gate_activation(input_act, value[u]);
                     if (rotated) {
                         const size_t at = (size_t)(position0 + t0 + u) * half + pair;
-                        value[u] = value[u] * cos_table[at] + sign * Num<T>::load(x + other) * sin_table[at];
+                        float partner = Num<T>::load(x + other);
+                        if (activated) partner = gate_activation(input_act, partner);
+                        value[u] = value[u] * cos_table[at] + sign * partner * sin_table[at];
                     }
                 }
             }
@@ -140,7 +150,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             } else {
                 const int pv = p - 2 * qk_pieces;
                 const bool is_gate = pv >= v_pieces;
-                if (kMode == kSummarise && is_gate) continue;
+                if (no_gate && is_gate) continue;
                 const int d = (is_gate ? pv - v_pieces : pv) * piece;
                 source = (is_gate ? g : v) + (size_t)head * value_dim + d;
                 c = 2 * head_dim + (is_gate ? value_dim : 0) + d;
@@ -166,8 +176,9 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             const bool is_qk = c < 2 * head_dim;
             const bool is_key = is_qk && c >= head_dim;
             const bool is_gate = !is_qk && c >= 2 * head_dim + value_dim;
-            if (kMode == kSummarise && ((is_qk && !is_key) || is_gate)) continue;
+            if ((kMode == kSummarise && is_qk && !is_key) || (no_gate && is_gate)) continue;
             const int d = is_qk ? (is_key ? c - head_dim : c) : 0;
+            const bool activated = input_act >= 0 && !is_gate;
             const bool rotated = is_qk && d < rotary_dim;
             const int pair = d < half ? d : d - half;
             const int other = c + (d < half ? half : -half);
@@ -177,7 +188,12 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             for (int u = 0; u < kTokens; ++u) {
                 if (u >= n) break;
                 float value = Num<T>::load(raw + u * row + c);
-                if (rotated) value = value * raw_cos[u * half + pair] + sign * Num<T>::load(raw + u * row + other) * raw_sin[u * half + pair];
+                if (activated) value = gate_activation(input_act, value);
+                if (rotated) {
+                    float partner = Num<T>::load(raw + u * row + other);
+                    if (activated) partner = gate_activation(input_act, partner);
+                    value = value * raw_cos[u * half + pair] + sign * partner * raw_sin[u * half + pair];
+                }
                 staged[(b * kTokens + u) * row + c] = value * factor;
             }
         }
@@ -246,6 +262,11 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         if (kMode != kSummarise) {
             for (int u = warp; u < n; u += warps) {  // a warp per token: root mean square of the head's o, gate, store
                 const float* o_row = results + u * value_dim;
+                if (raw_out != nullptr) {  // the caller norms and gates
+                    float* raw_row = raw_out + (size_t)(first + t0 + u) * raw_stride + (size_t)head * value_dim;
+                    for (int d = lane; d < value_dim; d += 32) raw_row[d] = o_row[d] * out_scale;
+                    continue;
+                }
                 const float* gate_row = group + u * row + 2 * head_dim + value_dim;
                 float ssq = 0.0f;
                 for (int d = lane; d < value_dim; d += 32) ssq = fmaf(o_row[d], o_row[d], ssq);
@@ -304,9 +325,44 @@ __global__ void retention_prefix_kernel(float* __restrict__ scratch, float* __re
     *stored = s;
 }
 
+// y[t] = raw[t] / sqrt(mean(raw[t]^2) + eps) * gain * act(gate[t]) over a whole row (all heads together);
+// gate_sigmoid != 0: sigmoid, else silu.  grid (rows); block 256.
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_norm_gate_kernel(const float* __restrict__ raw, int raw_stride, const float* __restrict__ gain, const T* __restrict__ gate,
+                       int gate_stride, T* __restrict__ out, int out_stride, int width, float eps, int gate_sigmoid) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float scratch[32];
+    const size_t row = blockIdx.x;
+    const float* mine = raw + row * raw_stride;
+    float ssq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) ssq = fmaf(mine[c], mine[c], ssq);
+    const float inverse = 1.0f / sqrtf(block_sum(ssq, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float g = Num<T>::load(gate + row * gate_stride + c);
+        const float s = 1.0f / (1.0f + expf(-g));
+        Num<T>::store(out + row * out_stride + c, mine[c] * inverse * gain[c] * (gate_sigmoid ? s : g * s));
+    }
+}
+
 }  // namespace mb
 
 using namespace mb;
+
+MB_EXPORT int mb_group_norm_gate(const float* raw, int raw_stride, const float* gain, const void* gate, int gate_stride, void* out,
+                                 int out_stride, int dtype, int rows, int width, float eps, int gate_sigmoid, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    if (dtype == MB_F32)
+        MB_LAUNCH("group_norm_gate", group_norm_gate_kernel<float>, dim3(rows), dim3(256), 0, stream, true, raw, raw_stride, gain,
+                  (const float*)gate, gate_stride, (float*)out, out_stride, width, eps, gate_sigmoid);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("group_norm_gate", group_norm_gate_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, true, raw, raw_stride, gain,
+                  (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, width, eps, gate_sigmoid);
+    else
+        return fail("group_norm_gate: unknown dtype code %d", dtype);
+    return 0;
+}
 
 // q, k: [tokens, >= heads * head_dim]; v, g: [tokens, >= heads * value_dim]; all four column slices of one tensor
 // (one row stride).  state: float [slots, heads, head_dim, value_dim]; slots[sequence] picks the row.
@@ -322,7 +378,8 @@ template <typename T, int kDim>
 int launch_retention(const void* q, const void* k, const void* v, const void* g, int in_stride, const int* positions,
                      const float* cos_table, const float* sin_table, int rotary_dim, const float* decay, float key_scale, float eps,
                      float* state, const int* slots, const int* cu_q, int sequences, int heads, int head_dim, int value_dim, void* out,
-                     int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, cudaStream_t stream, size_t smem) {
+                     int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, int input_act, float* raw_out,
+                     int raw_stride, cudaStream_t stream, size_t smem) {
     const dim3 block((value_dim + 31) / 32 * 32);
     const int runs = (run_length > 0 && max_q_len > run_length) ? (max_q_len + run_length - 1) / run_length : 1;
     // rows that cp.async can copy: every row and table row starts on 16 bytes and is whole 16-byte pieces
@@ -340,7 +397,7 @@ int launch_retention(const void* q, const void* k, const void* v, const void* g,
     MB_LAUNCH("retention_scan", (retention_scan_kernel<T, MODE, kDim>), dim3(heads, sequences, RUNS), dim3(block), smem, stream, true,  \
               (const T*)q, (const T*)k, (const T*)v, (const T*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,  \
               key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (T*)out, out_stride, out_scale, run_length, scratch, \
-              async_ok)
+              async_ok, input_act, raw_out, raw_stride)
     if (runs == 1) {
         MB_SCAN(kWhole, 1);
         return 0;
@@ -372,12 +429,16 @@ int pick_retention(int head_dim, int value_dim, size_t smem_shared, size_t smem_
 // (one row stride).  state: float [slots, heads, head_dim, value_dim]; slots[sequence] picks the row.
 // rotary_dim 0: no rotation (the tables may then be null).  With max_q_len > run_length > 0 the sequences are walked in
 // runs of run_length tokens at once, and scratch must hold mb_retention_scratch_floats floats.
+// input_act: -1, or a code of the activation table applied to q, k, v.  raw_out non-null: out_scale * o_t goes there as
+// floats ([tokens][raw_stride], heads side by side) and nothing else is written; g and out may then be null.
 MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, const void* g, int in_stride, int dtype,
                                 const int* positions, const float* cos_table, const float* sin_table, int rotary_dim,
                                 const float* decay, float key_scale, float eps, float* state, const int* slots, const int* cu_q,
                                 int sequences, int heads, int head_dim, int value_dim, void* out, int out_stride, float out_scale,
-                                int max_q_len, int run_length, float* scratch, cudaStream_t stream) {
+                                int max_q_len, int run_length, float* scratch, int input_act, float* raw_out, int raw_stride,
+                                cudaStream_t stream) {
     if (sequences <= 0 || heads <= 0) return 0;
+    if (input_act >= MB_ACT_COUNT) return fail("retention_scan: unknown activation code %d", input_act);
     if (head_dim <= 0 || value_dim <= 0 || value_dim > 1024) return fail("retention_scan: head_dim %d, value_dim %d (at most 1024)", head_dim, value_dim);
     if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim) return fail("retention_scan: rotary_dim %d must be even and at most %d", rotary_dim, head_dim);
     if (rotary_dim > 0 && (cos_table == nullptr || sin_table == nullptr)) return fail("retention_scan: rotation needs its tables");
@@ -394,11 +455,12 @@ MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, con
     if (dtype == MB_F32)
         status = pick_retention<float>(head_dim, value_dim, smem, smem_kept, q, k, v, g, in_stride, positions, cos_table, sin_table,
                                        rotary_dim, decay, key_scale, eps, state, slots, cu_q, sequences, heads, head_dim, value_dim, out,
-                                       out_stride, out_scale, max_q_len, run_length, scratch, stream);
+                                       out_stride, out_scale, max_q_len, run_length, scratch, input_act, raw_out, raw_stride, stream);
     else if (dtype == MB_BF16)
         status = pick_retention<__nv_bfloat16>(head_dim, value_dim, smem, smem_kept, q, k, v, g, in_stride, positions, cos_table, sin_table,
                                                rotary_dim, decay, key_scale, eps, state, slots, cu_q, sequences, heads, head_dim, value_dim,
-                                               out, out_stride, out_scale, max_q_len, run_length, scratch, stream);
+                                               out, out_stride, out_scale, max_q_len, run_length, scratch, input_act, raw_out, raw_stride,
+                                               stream);
     else
         return fail("retention_scan: unknown dtype code %d", dtype);
     return status ? status : check_launch("retention_scan");

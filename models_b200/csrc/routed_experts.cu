@@ -1,0 +1,506 @@
+// A mixture of experts: every token uses the `top` experts with the largest router logits.
+//
+//   router:   z = R x (float sums), the `top` largest (ties to the lower index), weights = softmax over the chosen z
+//   sort:     the (token, choice) entries grouped by expert, in token order, cut into tiles of 64 rows
+//   expert e: g = min(Wg_e x, limit), u = clamp(Wu_e x, -limit, limit), y = Wd_e (g * sigmoid(slope * g) * (u + 1))
+//   combine:  out[token] = sum_choice weight * y[token, choice] (+ sigmoid(score[token]) * shared[token])
+//
+// The two expert products are grouped products: a block owns one tile of one expert's rows and 64 output columns, reads
+// that expert's weights, and gathers (first product) or scatters (second product) its rows by the sorted list, so a
+// step of any size is three launches whose grids do not depend on how the router chose.  Every output is one chain of
+// sums in ascending k: a row's result does not depend on what else is in the batch.  Storage float or bfloat16,
+// arithmetic float; with bfloat16 storage and sizes that are multiples of 16 the products run on the tensor cores.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int kTileRows = 64;
+constexpr int kTileCols = 64;
+constexpr int kMaxTop = 32;
+
+__device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+__device__ __forceinline__ float clamped_swish(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoid(slope * g) * (u + 1.0f);
+}
+
+// grid (tokens); block 128.  shared: width floats (the token's row), experts floats (its logits).
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int* __restrict__ chosen,
+                   float* __restrict__ weights, int width, int experts, int top) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ float router_shared[];
+    float* row = router_shared;
+    float* logits = router_shared + width;
+    __shared__ float picked[kMaxTop];
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = Num<T>::load(x + (size_t)token * x_stride + c);
+    __syncthreads();
+    for (int e = warp; e < experts; e += warps) {
+        const T* w = router + (size_t)e * width;
+        float sum = 0.0f;
+        for (int c = lane; c < width; c += 32) sum = fmaf(row[c], Num<T>::load(w + c), sum);
+        sum = warp_sum(sum);
+        if (lane == 0) logits[e] = sum;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    for (int s = 0; s < top; ++s) {
+        // the largest logit that is not taken yet; ties go to the lower index (a taken expert's logit is -inf)
+        float best = -CUDART_INF_F;
+        int index = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = logits[e];
+            if (v > best || (v == best && e < index)) best = v, index = e;
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+            if (other > best || (other == best && other_index < index)) best = other, index = other_index;
+        }
+        if (index == 0x7fffffff) index = 0;  // (only if every logit is NaN)
+        if (lane == 0) {
+            chosen[(size_t)token * top + s] = index;
+            picked[s] = best;
+            logits[index] = -CUDART_INF_F;
+        }
+        __syncwarp();
+    }
+    __syncwarp();
+    if (lane == 0) {
+        const float top_logit = picked[0];  // the largest: the first one picked
+        float sum = 0.0f;
+        for (int s = 0; s < top; ++s) sum += expf(picked[s] - top_logit);
+        for (int s = 0; s < top; ++s) weights[(size_t)token * top + s] = expf(picked[s] - top_logit) / sum;
+    }
+}
+
+// One block of 1024 threads.  entries = tokens * top.  offsets [experts + 1]; sorted [entries]: entry ids (token * top +
+// choice) by expert, in ascending order within an expert; tile_expert / tile_row [max_tiles]: the expert (or -1) and the
+// first row of the sorted list of every tile of kTileRows rows.
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const int* __restrict__ chosen, int entries, int experts, int* __restrict__ offsets, int* __restrict__ sorted,
+                  int* __restrict__ tile_expert, int* __restrict__ tile_row, int max_tiles) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ int sort_shared[];  // counts [experts], starts [experts + 1]
+    int* counts = sort_shared;
+    int* starts = sort_shared + experts;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int e = warp; e < experts; e += warps) {
+        int count = 0;
+        for (int base = 0; base < entries; base += 32) {
+            const int i = base + lane;
+            count += __popc(__ballot_sync(0xffffffffu, i < entries && chosen[i] == e));
+        }
+        if (lane == 0) counts[e] = count;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < experts; ++e) {
+            starts[e] = at;
+            offsets[e] = at;
+            for (int r = 0; r < counts[e] && tile < max_tiles; r += kTileRows) {
+                tile_expert[tile] = e;
+                tile_row[tile] = at + r;
+                ++tile;
+            }
+            at += counts[e];
+        }
+        starts[experts] = at;
+        offsets[experts] = at;
+        for (; tile < max_tiles; ++tile) tile_expert[tile] = -1, tile_row[tile] = 0;
+    }
+    __syncthreads();
+    for (int e = warp; e < experts; e += warps) {
+        int at = starts[e];
+        for (int base = 0; base < entries; base += 32) {
+            const int i = base + lane;
+            const bool hit = i < entries && chosen[i] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) sorted[at + __popc(mask & ((1u << lane) - 1u))] = i;
+            at += __popc(mask);
+        }
+    }
+}
+
+// The grouped product in plain float arithmetic.  grid (ceil(N / 64), max_tiles); block 256 (16 x 16; a thread 4 x 4).
+// kFirst: a = x [tokens][K], rows gathered through the sorted list (token = entry / top); two weight sets [experts][N][K]
+//         (gate, up); mid [entries][N] (sorted order) = clamped_swish(gate . x, up . x).
+// else:   a = mid [entries][K] in sorted order; one weight set (down); slot_out [entry][N] (float), scattered by entry id.
+template <typename T, bool kFirst>
+__global__ void __launch_bounds__(256)
+expert_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0, const T* __restrict__ w1,
+                      T* __restrict__ mid, float* __restrict__ slot_out, int out_stride, const int* __restrict__ sorted,
+                      const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row,
+                      int top, int N, int K, float limit, float slope) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    constexpr int kStep = 16;
+    __shared__ float a_tile[kStep][kTileRows + 4];
+    __shared__ float b_tile[kFirst ? 2 : 1][kStep][kTileCols + 4];
+    __shared__ int source_row[kTileRows];
+    const int expert = tile_expert[blockIdx.y];
+    if (expert < 0) return;  // the whole block leaves
+    const int row0 = tile_row[blockIdx.y];
+    const int rows = min(kTileRows, offsets[expert + 1] - row0);
+    const int n0 = blockIdx.x * kTileCols;
+    if (threadIdx.x < kTileRows) {
+        const int r = threadIdx.x;
+        source_row[r] = r < rows ? (kFirst ? sorted[row0 + r] / top : row0 + r) : -1;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int load_row = threadIdx.x >> 2, load_k = (threadIdx.x & 3) * 4;
+    const T* w0_e = w0 + (size_t)expert * N * K;
+    const T* w1_e = kFirst ? w1 + (size_t)expert * N * K : nullptr;
+    float acc[kFirst ? 2 : 1][4][4];
+#pragma unroll
+    for (int s = 0; s < (kFirst ? 2 : 1); ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[s][i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += kStep) {
+        const int src = source_row[load_row];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = k0 + load_k + j;
+            a_tile[load_k + j][load_row] = (src >= 0 && k < K) ? Num<T>::load(a + (size_t)src * a_stride + k) : 0.0f;
+            const int n = n0 + load_row;
+            b_tile[0][load_k + j][load_row] = (n < N && k < K) ? Num<T>::load(w0_e + (size_t)n * K + k) : 0.0f;
+            if (kFirst) b_tile[kFirst ? 1 : 0][load_k + j][load_row] = (n < N && k < K) ? Num<T>::load(w1_e + (size_t)n * K + k) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kStep; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&a_tile[kk][ty * 4]);
+            const float ar[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int s = 0; s < (kFirst ? 2 : 1); ++s) {
+                const float4 bv = *reinterpret_cast<const float4*>(&b_tile[s][kk][tx * 4]);
+                const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[s][i][j] = fmaf(ar[i], br[j], acc[s][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (kFirst)
+                Num<T>::store(mid + (size_t)(row0 + r) * out_stride + n, clamped_swish(acc[0][i][j], acc[kFirst ? 1 : 0][i][j], limit, slope));
+            else
+                slot_out[(size_t)sorted[row0 + r] * out_stride + n] = acc[0][i][j];
+        }
+    }
+}
+
+// The same on the tensor cores: bfloat16, K a multiple of 16, rows of a and of the weights starting on 16 bytes.
+// Block 128: warp w owns rows 16w .. 16w + 15 of the tile and all 64 columns; K in steps of 64 through two stages of
+// cp.async copies (rows padded by 16 bytes so that ldmatrix reads without bank conflicts); m16n8k16 products, float sums.
+namespace tc {
+
+using bf16 = __nv_bfloat16;
+constexpr int kStepK = 64;
+constexpr int kRowBytes = kStepK * 2 + 16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool kFirst>
+__global__ void __launch_bounds__(128)
+expert_product_tc_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                         bf16* __restrict__ mid, float* __restrict__ slot_out, int out_stride, const int* __restrict__ sorted,
+                         const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row,
+                         int top, int N, int K, float limit, float slope) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    constexpr int kSets = kFirst ? 2 : 1;
+    constexpr int kTileBytes = kTileRows * kRowBytes;
+    constexpr int kStageBytes = (1 + kSets) * kTileBytes;
+    extern __shared__ __align__(16) unsigned char tc_smem[];
+    __shared__ int source_row[kTileRows];
+    const int expert = tile_expert[blockIdx.y];
+    if (expert < 0) return;
+    const int row0 = tile_row[blockIdx.y];
+    const int rows = min(kTileRows, offsets[expert + 1] - row0);
+    const int n0 = blockIdx.x * kTileCols;
+    if (threadIdx.x < kTileRows) {
+        const int r = threadIdx.x;
+        source_row[r] = r < rows ? (kFirst ? sorted[row0 + r] / top : row0 + r) : -1;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
+    const bf16* w_e[kSets];
+    w_e[0] = w0 + (size_t)expert * N * K;
+    if (kFirst) w_e[kSets - 1] = w1 + (size_t)expert * N * K;
+    const uint32_t base = smem_u32(tc_smem);
+    const int steps = (K + kStepK - 1) / kStepK;
+    auto load_stage = [&](int step, int stage) {
+        const int k0 = step * kStepK;
+        const uint32_t at = base + stage * kStageBytes;
+        for (int i = threadIdx.x; i < kTileRows * 8; i += 128) {
+            const int r = i >> 3, piece = i & 7;
+            const int k = k0 + piece * 8;
+            const int src = source_row[r];
+            const bool a_ok = src >= 0 && k < K;
+            cp_async16(at + r * kRowBytes + piece * 16, a_ok ? a + (size_t)src * a_stride + k : a, a_ok);
+            const int n = n0 + r;
+            const bool w_ok = n < N && k < K;
+#pragma unroll
+            for (int s = 0; s < kSets; ++s)
+                cp_async16(at + (1 + s) * kTileBytes + r * kRowBytes + piece * 16, w_ok ? w_e[s] + (size_t)n * K + k : w_e[s], w_ok);
+        }
+    };
+    float acc[kSets][8][4];
+#pragma unroll
+    for (int s = 0; s < kSets; ++s)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) acc[s][nt][0] = acc[s][nt][1] = acc[s][nt][2] = acc[s][nt][3] = 0.0f;
+    load_stage(0, 0);
+    cp_async_commit();
+    for (int step = 0; step < steps; ++step) {
+        const int stage = step & 1;
+        if (step + 1 < steps) {
+            load_stage(step + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t a_at = base + stage * kStageBytes + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kRowBytes + (lane >> 4) * 16;
+#pragma unroll
+        for (int ks = 0; ks < kStepK / 16; ++ks) {
+            uint32_t af[4];
+            ldmatrix_x4(af, a_at + ks * 32);
+#pragma unroll
+            for (int s = 0; s < kSets; ++s) {
+                const uint32_t w_at = base + stage * kStageBytes + (1 + s) * kTileBytes;
+#pragma unroll
+                for (int part = 0; part < 4; ++part) {
+                    uint32_t b[4];
+                    const int w_row = part * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+                    ldmatrix_x4(b, w_at + w_row * kRowBytes + (ks * 2 + ((lane >> 3) & 1)) * 16);
+                    mma_bf16(acc[s][2 * part], af, b[0], b[1]);
+                    mma_bf16(acc[s][2 * part + 1], af, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + group_id + 8 * half;
+        if (r >= rows) continue;
+        const size_t out_row = kFirst ? (size_t)(row0 + r) : (size_t)sorted[row0 + r];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int n = n0 + nt * 8 + tid4 * 2 + c;
+                if (n >= N) continue;
+                const float v0 = acc[0][nt][2 * half + c];
+                if (kFirst)
+                    mid[out_row * out_stride + n] = __float2bfloat16_rn(clamped_swish(v0, acc[kSets - 1][nt][2 * half + c], limit, slope));
+                else
+                    slot_out[out_row * out_stride + n] = v0;
+            }
+        }
+    }
+}
+
+}  // namespace tc
+
+// out[t][c] = clamped_swish(gate[t][c], up[t][c]); grid (ceil(rows * cols / 256)); block 256.
+template <typename T>
+__global__ void clamped_swish_kernel(const T* __restrict__ gate, const T* __restrict__ up, int in_stride, T* __restrict__ out,
+                                     int out_stride, size_t total, int cols, float limit, float slope) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / cols;
+    const int c = (int)(i % cols);
+    Num<T>::store(out + t * out_stride + c,
+                  clamped_swish(Num<T>::load(gate + t * in_stride + c), Num<T>::load(up + t * in_stride + c), limit, slope));
+}
+
+// out[t][c] = sum_s weights[t][s] * slot_out[t * top + s][c] (+ sigmoid(score[t]) * shared[t][c]); float out.
+template <typename T>
+__global__ void expert_combine_kernel(const float* __restrict__ slot_out, const float* __restrict__ weights,
+                                      const float* __restrict__ shared, const T* __restrict__ score, int score_stride,
+                                      float* __restrict__ out, size_t total, int width, int top) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / width;
+    const int c = (int)(i % width);
+    float sum = 0.0f;
+    for (int s = 0; s < top; ++s) sum = fmaf(weights[t * top + s], slot_out[(t * top + s) * width + c], sum);
+    if (shared != nullptr) sum = fmaf(sigmoid(Num<T>::load(score + t * score_stride)), shared[i], sum);
+    out[i] = sum;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_route_tile_rows() { return kTileRows; }
+MB_EXPORT int mb_route_max_top() { return kMaxTop; }
+
+MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, int dtype, int* chosen, float* weights, int tokens,
+                             int width, int experts, int top, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > kMaxTop)
+        return fail("router_topk: width %d, %d experts, top %d (at most %d and the number of experts)", width, experts, top, kMaxTop);
+    const size_t smem = ((size_t)width + experts) * sizeof(float);
+    if (smem > 200 * 1024) return fail("router_topk: a row of %d and %d logits exceed a block's shared memory", width, experts);
+    if (dtype == MB_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("router_topk", router_topk_kernel<float>, dim3(tokens), dim3(128), smem, stream, true, (const float*)x, x_stride,
+                  (const float*)router, chosen, weights, width, experts, top);
+    } else if (dtype == MB_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("router_topk", router_topk_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, stream, true, (const __nv_bfloat16*)x,
+                  x_stride, (const __nv_bfloat16*)router, chosen, weights, width, experts, top);
+    } else {
+        return fail("router_topk: unknown dtype code %d", dtype);
+    }
+    return 0;
+}
+
+MB_EXPORT int mb_route_max_tiles(int entries, int experts) { return (entries + kTileRows - 1) / kTileRows + experts; }
+
+MB_EXPORT int mb_route_sort(const int* chosen, int entries, int experts, int* offsets, int* sorted, int* tile_expert, int* tile_row,
+                            int max_tiles, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (experts <= 0 || experts > 4096) return fail("route_sort: %d experts (at most 4096)", experts);
+    if (max_tiles < mb_route_max_tiles(entries, experts)) return fail("route_sort: room for %d tiles, %d may be needed", max_tiles, mb_route_max_tiles(entries, experts));
+    MB_LAUNCH("route_sort", route_sort_kernel, dim3(1), dim3(1024), (2 * (size_t)experts + 1) * sizeof(int), stream, true, chosen, entries,
+              experts, offsets, sorted, tile_expert, tile_row, max_tiles);
+    return 0;
+}
+
+// first != 0: a = x [tokens][K] gathered, w0 / w1 = gate / up [experts][N][K], mid [entries][N] written (storage type).
+// first == 0: a = mid [entries][K], w0 = down [experts][N][K], slot_out [entries][N] (float) written by entry id.
+MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, const void* w1, void* mid, float* slot_out, int out_stride,
+                                int dtype, const int* sorted, const int* offsets, const int* tile_expert, const int* tile_row,
+                                int max_tiles, int top, int N, int K, float limit, float slope, int first, int tensor_cores,
+                                cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    if (N <= 0 || K <= 0 || top <= 0) return fail("expert_product: N %d, K %d, top %d", N, K, top);
+    if (max_tiles > 65535) return fail("expert_product: %d tiles exceed the grid limit 65535", max_tiles);
+    const dim3 grid((N + kTileCols - 1) / kTileCols, max_tiles);
+    if (tensor_cores && dtype == MB_BF16 && K % 8 == 0 && a_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w0 & 15) &&
+        !((uintptr_t)w1 & 15)) {
+        using namespace tc;
+        if (first) {
+            const size_t smem = 2 * 3 * (size_t)kTileRows * kRowBytes;
+            static bool configured = false;
+            if (!configured) {
+                cudaError_t status = cudaFuncSetAttribute(expert_product_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (status != cudaSuccess) return fail("expert_product: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+                configured = true;
+            }
+            MB_LAUNCH("expert_product_tc", expert_product_tc_kernel<true>, grid, dim3(128), smem, stream, true, (const bf16*)a, a_stride,
+                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope);
+        } else {
+            const size_t smem = 2 * 2 * (size_t)kTileRows * kRowBytes;
+            static bool configured = false;
+            if (!configured) {
+                cudaError_t status = cudaFuncSetAttribute(expert_product_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (status != cudaSuccess) return fail("expert_product: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+                configured = true;
+            }
+            MB_LAUNCH("expert_product_tc", expert_product_tc_kernel<false>, grid, dim3(128), smem, stream, true, (const bf16*)a, a_stride,
+                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope);
+        }
+        return 0;
+    }
+#define MB_PRODUCT(T, FIRST)                                                                                                        \
+    MB_LAUNCH("expert_product", (expert_product_kernel<T, FIRST>), grid, dim3(256), 0, stream, true, (const T*)a, a_stride, (const T*)w0, \
+              (const T*)w1, (T*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope)
+    if (dtype == MB_F32) {
+        if (first) MB_PRODUCT(float, true); else MB_PRODUCT(float, false);
+    } else if (dtype == MB_BF16) {
+        if (first) MB_PRODUCT(__nv_bfloat16, true); else MB_PRODUCT(__nv_bfloat16, false);
+    } else {
+        return fail("expert_product: unknown dtype code %d", dtype);
+    }
+#undef MB_PRODUCT
+    return 0;
+}
+
+MB_EXPORT int mb_clamped_swish(const void* gate, const void* up, int in_stride, void* out, int out_stride, int dtype, int rows, int cols,
+                               float limit, float slope, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    const size_t total = (size_t)rows * cols;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    if (dtype == MB_F32)
+        MB_LAUNCH("clamped_swish", clamped_swish_kernel<float>, grid, dim3(256), 0, stream, true, (const float*)gate, (const float*)up, in_stride,
+                  (float*)out, out_stride, total, cols, limit, slope);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("clamped_swish", clamped_swish_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, (const __nv_bfloat16*)gate,
+                  (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, out_stride, total, cols, limit, slope);
+    else
+        return fail("clamped_swish: unknown dtype code %d", dtype);
+    return 0;
+}
+
+// shared may be null (no shared expert); score is one number per token of the storage type `dtype` (stride in elements).
+MB_EXPORT int mb_expert_combine(const float* slot_out, const float* weights, const float* shared, const void* score, int score_stride,
+                                int dtype, float* out, int tokens, int width, int top, cudaStream_t stream) {
+    if (tokens <= 0 || width <= 0) return 0;
+    if (shared != nullptr && score == nullptr) return fail("expert_combine: a shared expert needs its gate scores");
+    const size_t total = (size_t)tokens * width;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    if (dtype == MB_F32)
+        MB_LAUNCH("expert_combine", expert_combine_kernel<float>, grid, dim3(256), 0, stream, true, slot_out, weights, shared, (const float*)score,
+                  score_stride, out, total, width, top);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("expert_combine", expert_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, slot_out, weights, shared,
+                  (const __nv_bfloat16*)score, score_stride, out, total, width, top);
+    else
+        return fail("expert_combine: unknown dtype code %d", dtype);
+    return 0;
+}

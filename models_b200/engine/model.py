@@ -11,6 +11,7 @@ from typing import Callable, Dict, List, Mapping, Optional
 import torch
 
 from ..config.specs import ModelSpec
+from ..kernels import ops
 from ..parts import RunContext, Runtime, as_delta, build_part
 from ..weights.loader import ParamRequest, check_names_and_shapes
 
@@ -82,6 +83,9 @@ class DecoderModel:
             if logits is not None:
                 return logits
         x = self.embedding.forward(batch.tokens)
+        streams = self.spec.residual_streams
+        if streams > 1:
+            x = ops.stream_copies(x, streams)  # [tokens, streams * width]: every copy starts as the embedding's row
         pending = None
         schedule = self.spec.schedule
         for index, (run, entry) in enumerate(zip(runs, schedule)):
@@ -95,9 +99,12 @@ class DecoderModel:
                 pending = block.forward(x, as_delta(pending), batch, run)
             if self.observer is not None:
                 delta = as_delta(pending)
-                self.observer(run.run, x + delta.float() if delta is not None else x.clone())
+                seen = ops.stream_sum(x, self.spec.hidden_size) if streams > 1 else x
+                self.observer(run.run, seen + delta.float() if delta is not None else seen.clone())
         if batch.num_wanted == 0:
             return None
+        if streams > 1:
+            x = ops.stream_sum(x, self.spec.hidden_size)  # the copies added up: what the final norm reads
         if getattr(self.head, "takes_prenormed", False):
             every_row = batch.max_q_len == 1 and batch.num_wanted == batch.num_tokens
             return self.head.forward(x, pending, self.final_norm, batch.want_rows, every_row)

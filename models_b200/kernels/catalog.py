@@ -14,6 +14,8 @@ LIBRARIES = [
     ("mb_gated_recurrence", ["gated_recurrence.cu"], {}),
     ("mb_gated_attention", ["gated_attention.cu"], {}),
     ("mb_retention", ["retention.cu"], {}),
+    ("mb_hyper_streams", ["hyper_streams.cu"], {}),
+    ("mb_routed_experts", ["routed_experts.cu"], {}),
     # the tensor-core form is compiled per (key size, value size, values read from the key rows) at first use; these
     # are the sizes of the benchmark's models of the design that uses it
     ("mb_gated_attention_tc", ["gated_attention_tc.cu"], {"MB_KEY_DIM": 64, "MB_VALUE_DIM": 128, "MB_SHARED_ROWS": 0}),

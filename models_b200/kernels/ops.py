@@ -548,6 +548,43 @@ def norm_store(q: Optional[torch.Tensor], k: torch.Tensor, v: Optional[torch.Ten
                                 page_size, _stream()))
 
 
+def rotate_norm_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                      sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, unit_norm: bool, eps: float,
+                      value_cos: Optional[torch.Tensor], value_sin: Optional[torch.Tensor], value_rotary_dim: int,
+                      k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch.Tensor, heads: int, kv_heads: int,
+                      head_dim: int, value_dim: int) -> None:
+    """Per head: q (in place) and k (into the key pool at `slot_mapping`) are rotated by the token's position over their
+    first `rotary_dim` coordinates (float32 tables [positions, rotary_dim / 2]; pairs (i, i + rotary_dim / 2), or
+    (2i, 2i + 1) when `interleaved`) and then, with `unit_norm`, divided by sqrt(mean(x^2) + eps) over the head; v is rotated
+    over its first `value_rotary_dim` coordinates by tables of its own and stored in the value pool.  q, k, v may be column
+    slices of one tensor.  Heads of up to 256 coordinates."""
+    _cuda(q, k, v, positions, cos, sin, value_cos, value_sin, k_pool, v_pool, slot_mapping)
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    tokens = k.shape[0]
+    for name, t, width in (("q", q, heads * head_dim), ("k", k, kv_heads * head_dim), ("v", v, kv_heads * value_dim)):
+        _columns(t, name)
+        if t.shape[1] != width or t.shape[0] != tokens or t.dtype != k.dtype:
+            raise KernelError(f"rotate_norm_store: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {k.dtype} is needed")
+    for name, dim, tables in (("rotary_dim", rotary_dim, (cos, sin)), ("value_rotary_dim", value_rotary_dim, (value_cos, value_sin))):
+        if dim:
+            for table in tables:
+                if table is None or table.dtype != torch.float32 or table.dim() != 2 or table.shape[1] * 2 != dim or not table.is_contiguous():
+                    raise KernelError(f"rotate_norm_store: {name} {dim} needs contiguous float32 tables [positions, {dim // 2}]")
+    page_size = k_pool.shape[2]
+    if tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or not k_pool.is_contiguous() or k_pool.dtype != k.dtype:
+        raise KernelError(f"rotate_norm_store: the key pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}] of {k.dtype}")
+    if tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim) or not v_pool.is_contiguous() or v_pool.dtype != k.dtype:
+        raise KernelError(f"rotate_norm_store: the value pool must be contiguous [pages, {kv_heads}, page_size, {value_dim}] of {k.dtype}")
+    lib = gated_attention_library()
+    _run(lib, lib.mb_rotate_norm_store(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _code(k.dtype), _p(positions),
+                                       _p(cos) if rotary_dim else None, _p(sin) if rotary_dim else None, int(rotary_dim),
+                                       1 if interleaved else 0, 1 if unit_norm else 0, ctypes.c_float(eps),
+                                       _p(value_cos) if value_rotary_dim else None, _p(value_sin) if value_rotary_dim else None,
+                                       int(value_rotary_dim), _p(k_pool), _p(v_pool), _p(slot_mapping), tokens, heads, kv_heads,
+                                       head_dim, value_dim, page_size, _stream()))
+
+
 GATE_KINDS = {None: 0, "head": 1, "element": 2}
 
 
@@ -589,12 +626,18 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
                     block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
                     kv_heads: int, head_dim: int, value_dim: int, weights: str, scale: float, slope_exponent: float = 0.0,
                     head_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                    gate_kind: Optional[str] = None, kernel: Optional[str] = None) -> None:
+                    gate_kind: Optional[str] = None, kernel: Optional[str] = None, head_scale: Optional[torch.Tensor] = None,
+                    softcap: float = 0.0, sink: bool = False, turn_cos: Optional[torch.Tensor] = None,
+                    turn_sin: Optional[torch.Tensor] = None) -> None:
     """Causal attention over the paged cache with `weights` "softmax" or "sigmoid" (independent sigmoids of the scores,
     not normalised over keys); score = scale * q.k - 2^(-slope_exponent (h + 1) / heads) * (i - j) + head_bias[h]
     (slope_exponent 0: no distance term; head_bias None: 0).  `v_pool` None: the values are the first `value_dim`
     coordinates of the key rows.  gate_kind "head": out_h *= sigmoid(gate[:, h]); "element": out *= sigmoid(gate),
     gate [T, heads * value_dim].  q [T, heads * head_dim], out [T, heads * value_dim] and gate may be column slices.
+    `head_scale` [heads] float32: score = scale * head_scale[h] * q.k ...; `softcap` c > 0: the score, after everything
+    else, becomes c * tanh(score / c); `sink`: the softmax's denominator has one more term of score 0 without a value;
+    `turn_cos`, `turn_sin` (float32 [positions, value_dim / 2]): the values were stored rotated by their own positions
+    (pairs 2m, 2m + 1), and every head's sum is turned back by the query's position before any gate.
     `kernel`: None picks the decode form for steps of one token per sequence (the keys cut into runs with a block each;
     the grid follows the page table's width, not the lengths, so that a captured step stays valid), the tensor-core form
     where it applies (bfloat16 steps of many tokens), else the form with a warp per (token, head); "decode", "tc" or
@@ -630,6 +673,18 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
         _columns(gate, "gate")
         if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads if gate_kind == "head" else heads * value_dim):
             raise KernelError(f"gated_attention: a gate of kind {gate_kind!r} cannot be {tuple(gate.shape)} {gate.dtype}")
+    if head_scale is not None and (head_scale.dtype != torch.float32 or head_scale.numel() != heads or not head_scale.is_contiguous()):
+        raise KernelError(f"gated_attention: head_scale must be contiguous float32 of {heads} elements")
+    if (turn_cos is None) != (turn_sin is None):
+        raise KernelError("gated_attention: turning the result back needs both tables")
+    if turn_cos is not None:
+        _cuda(turn_cos, turn_sin)
+        for table in (turn_cos, turn_sin):
+            if table.dtype != torch.float32 or table.dim() != 2 or table.shape[1] * 2 != value_dim or not table.is_contiguous():
+                raise KernelError(f"gated_attention: the tables that turn the result back must be contiguous float32 [positions, {value_dim // 2}]")
+    if sink and weights != "softmax":
+        raise KernelError("gated_attention: a sink belongs to softmax weights")
+    extras = (_p(head_scale), ctypes.c_float(softcap), 1 if sink else 0, _p(turn_cos), _p(turn_sin))
     softmax = 1 if weights == "softmax" else 0
     sequences = kv_lens.numel()
     gate_stride = gate.stride(0) if gate is not None else 0
@@ -645,7 +700,7 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
             _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(values), values.shape[3], _p(block_table),
             block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences,
             heads, kv_heads, head_dim, value_dim, page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent), runs,
-            span, _p(scratch), _stream()))
+            span, _p(scratch), *extras, _stream()))
         _launches[0] += 1  # two kernels
         return
     if kernel == "tc" or (kernel is None and gated_attention_tc_takes(q, out, k_pool, head_dim, value_dim, max_q_len, gate, gate_kind)):
@@ -655,14 +710,14 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
         _run(lib, lib.mb_gated_attention_tc(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(values), _p(block_table), block_table.shape[1], _p(cu_q),
             _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences, max_q_len, heads, kv_heads,
-            page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent), _stream()))
+            page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent), *extras, _stream()))
         return
     lib = gated_attention_library()
     _run(lib, lib.mb_gated_attention_rows(
         _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(values), values.shape[3], _p(block_table),
         block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences,
         max_q_len, heads, kv_heads, head_dim, value_dim, page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent),
-        _stream()))
+        *extras, _stream()))
 
 
 def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, gate: Optional[torch.Tensor] = None,
@@ -700,22 +755,35 @@ def retention_library():
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, positions: torch.Tensor,
                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, decay: torch.Tensor,
                    key_scale: float, eps: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, heads: int,
-                   head_dim: int, value_dim: int, out: torch.Tensor, out_scale: float = 1.0, max_q_len: int = 1,
-                   run_length: Optional[int] = None) -> None:
+                   head_dim: int, value_dim: int, out: Optional[torch.Tensor], out_scale: float = 1.0, max_q_len: int = 1,
+                   run_length: Optional[int] = None, input_activation: Optional[str] = None,
+                   raw_out: Optional[torch.Tensor] = None) -> None:
     """Retention over the new tokens of every sequence: q and k rotated over their first `rotary_dim` coordinates
     (split-half pairs, float32 tables by position), k times key_scale; S = decay_h S + k v^T from the sequence's row of
     `state` (float32 [slots, heads, head_dim, value_dim], updated in place); o = S^T q; out = out_scale * o / rms(o) *
     silu(g) per head, rms(o) = sqrt(mean(o^2) + eps).  q, k, v, g are column slices with one row stride.
     Of `positions` only each sequence's first entry is read: its new tokens stand at consecutive positions.
+    `input_activation` (a name of the activation table): q, k and v pass it as they are read.  `raw_out` (float32
+    [tokens, heads * value_dim], may be a column slice): out_scale * o is written there and nothing else (no norm, no gate;
+    `g` and `out` may then be None) -- what follows is the caller's, for instance `group_norm_gate`.
     `max_q_len`: the most new tokens of any sequence.  Beyond `run_length` tokens (None: RETENTION_RUN once a step brings
     more than twice as many) the sequences are walked in runs of that many tokens at once, through scratch memory."""
-    _cuda(q, k, v, g, positions, cos, sin, decay, state, slots, cu_q, out)
+    _cuda(q, k, v, g, positions, cos, sin, decay, state, slots, cu_q, out, raw_out)
     _int32(positions, "positions")
     _int32(slots, "slots")
     _int32(cu_q, "cu_q")
     tokens = q.shape[0]
+    if raw_out is not None:
+        _columns(raw_out, "raw_out")
+        if raw_out.dtype != torch.float32 or tuple(raw_out.shape) != (tokens, heads * value_dim):
+            raise KernelError(f"retention_scan: raw_out must be float32 [{tokens}, {heads * value_dim}]")
+        g = v if g is None else g  # (not read)
+    elif g is None or out is None:
+        raise KernelError("retention_scan: without raw_out the gate rows and `out` are needed")
     for name, t, width in (("q", q, heads * head_dim), ("k", k, heads * head_dim), ("v", v, heads * value_dim),
                            ("g", g, heads * value_dim), ("out", out, heads * value_dim)):
+        if t is None:
+            continue
         _columns(t, name)
         if tuple(t.shape) != (tokens, width) or t.dtype != q.dtype:
             raise KernelError(f"retention_scan: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {q.dtype} is needed")
@@ -739,10 +807,33 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.T
     scratch = torch.empty((floats,), dtype=torch.float32, device=q.device) if floats else None
     _run(lib, lib.mb_retention_scan(_p(q), _p(k), _p(v), _p(g), q.stride(0), _code(q.dtype), _p(positions), _p(cos), _p(sin),
                                     rotary_dim, _p(decay), ctypes.c_float(key_scale), ctypes.c_float(eps), _p(state), _p(slots),
-                                    _p(cu_q), sequences, heads, head_dim, value_dim, _p(out), out.stride(0),
-                                    ctypes.c_float(out_scale), max_q_len, run_length, _p(scratch), _stream()))
+                                    _p(cu_q), sequences, heads, head_dim, value_dim, _p(out), out.stride(0) if out is not None else 0,
+                                    ctypes.c_float(out_scale), max_q_len, run_length, _p(scratch),
+                                    activation_code(input_activation) if input_activation is not None else -1, _p(raw_out),
+                                    raw_out.stride(0) if raw_out is not None else 0, _stream()))
     if floats:
         _launches[0] += 2  # three kernels
+
+
+def group_norm_gate(raw: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, eps: float,
+                    gate_activation: str = "sigmoid") -> None:
+    """out = raw / sqrt(mean(raw^2) + eps) * gain * act(gate) over whole rows (all heads together): raw float32, gain
+    float32 [width], gate and out of one storage type; all three may be column slices.  act: "sigmoid" or "silu"."""
+    if gate_activation not in ("sigmoid", "silu"):
+        raise KernelError(f"group_norm_gate: the gate's activation must be 'sigmoid' or 'silu', got {gate_activation!r}")
+    _cuda(raw, gain, gate, out)
+    for name, t in (("raw", raw), ("gate", gate), ("out", out)):
+        _columns(t, name)
+    rows, width = raw.shape
+    if raw.dtype != torch.float32 or gate.shape != raw.shape or out.shape != raw.shape or gate.dtype != out.dtype:
+        raise KernelError(f"group_norm_gate: raw {tuple(raw.shape)} {raw.dtype}, gate {tuple(gate.shape)} {gate.dtype}, out "
+                          f"{tuple(out.shape)} {out.dtype} do not fit")
+    if gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous():
+        raise KernelError(f"group_norm_gate: gain must be contiguous float32 of {width} elements")
+    lib = retention_library()
+    _run(lib, lib.mb_group_norm_gate(_p(raw), raw.stride(0), _p(gain), _p(gate), gate.stride(0), _p(out), out.stride(0),
+                                     _code(out.dtype), rows, width, ctypes.c_float(eps), 1 if gate_activation == "sigmoid" else 0,
+                                     _stream()))
 
 
 def gated_recurrence_library():
@@ -1388,4 +1479,198 @@ def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch
                                  history.stride(0) if history is not None else 0, _p(history_rows), 1 if append else 0,
                                  _p(history_len), _p(seeds),
                                  _p(counters), _p(uniforms), _p(out), int(max_candidates), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------ several residual streams
+
+def hyper_streams_library():
+    return load_library("mb_hyper_streams", ["hyper_streams.cu"])
+
+
+def _streams_of(x: torch.Tensor, width: int, name: str) -> int:
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or x.shape[1] % width:
+        raise KernelError(f"{name}: the streams must be contiguous float32 [tokens, streams * {width}], got {tuple(x.shape)} {x.dtype}")
+    return x.shape[1] // width
+
+
+def stream_copies(x: torch.Tensor, streams: int) -> torch.Tensor:
+    """[tokens, streams * width] float32 whose every copy is x [tokens, width]."""
+    _cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("stream_copies: x must be contiguous float32 [tokens, width]")
+    out = torch.empty((x.shape[0], streams * x.shape[1]), dtype=torch.float32, device=x.device)
+    lib = hyper_streams_library()
+    _run(lib, lib.mb_stream_copies(_p(x), _p(out), x.shape[0], x.shape[1], streams, _stream()))
+    return out
+
+
+def stream_sum(x: torch.Tensor, width: int) -> torch.Tensor:
+    """The copies of x [tokens, streams * width] added up: [tokens, width] float32."""
+    _cuda(x)
+    streams = _streams_of(x, width, "stream_sum")
+    out = torch.empty((x.shape[0], width), dtype=torch.float32, device=x.device)
+    lib = hyper_streams_library()
+    _run(lib, lib.mb_stream_sum(_p(x), _p(out), x.shape[0], width, streams, _stream()))
+    return out
+
+
+def hyper_read_norm(x: torch.Tensor, coefficients: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """u = sum_s coefficients[s] x_s over the copies of x [tokens, streams * width]; returns u / sqrt(mean(u^2) + eps) * gain
+    as [tokens, width] of `out_dtype`.  All arithmetic float32."""
+    _cuda(x, coefficients, gain)
+    width = gain.numel()
+    streams = _streams_of(x, width, "hyper_read_norm")
+    if coefficients.dtype != torch.float32 or coefficients.numel() != streams or not coefficients.is_contiguous() \
+            or gain.dtype != torch.float32 or not gain.is_contiguous():
+        raise KernelError(f"hyper_read_norm: {streams} float32 coefficients and a float32 gain are needed")
+    out = torch.empty((x.shape[0], width), dtype=out_dtype, device=x.device)
+    lib = hyper_streams_library()
+    _run(lib, lib.mb_hyper_read_norm(_p(x), _p(coefficients), _p(gain), _p(out), _code(out_dtype), x.shape[0], width, streams,
+                                     ctypes.c_float(eps), _stream()))
+    return out
+
+
+def hyper_write(x: torch.Tensor, y: torch.Tensor, out_coefficients: torch.Tensor, mix: torch.Tensor) -> None:
+    """All copies of x [tokens, streams * width] at once from the old ones: x_t <- sum_s mix[s, t] x_s + out_coefficients[t] * y
+    for y [tokens, width] (float32 or bfloat16, may be a column slice)."""
+    _cuda(x, y, out_coefficients, mix)
+    _columns(y, "y")
+    width = y.shape[1]
+    streams = _streams_of(x, width, "hyper_write")
+    if y.shape[0] != x.shape[0]:
+        raise KernelError(f"hyper_write: y {tuple(y.shape)} does not fit the streams {tuple(x.shape)}")
+    for name, t, count in (("out_coefficients", out_coefficients, streams), ("mix", mix, streams * streams)):
+        if t.dtype != torch.float32 or t.numel() != count or not t.is_contiguous():
+            raise KernelError(f"hyper_write: {name} must be contiguous float32 of {count} elements")
+    lib = hyper_streams_library()
+    _run(lib, lib.mb_hyper_write(_p(x), _p(y), y.stride(0), _code(y.dtype), _p(out_coefficients), _p(mix), x.shape[0], width, streams,
+                                 _stream()))
+
+
+def hyper_max_streams() -> int:
+    return hyper_streams_library().mb_hyper_max_streams()
+
+
+# ------------------------------------------------------------------------------------ routed experts
+
+def routed_experts_library():
+    return load_library("mb_routed_experts", ["routed_experts.cu"])
+
+
+def router_topk(x: torch.Tensor, router: torch.Tensor, top: int):
+    """Router logits z = router . x in float32 sums; per token the `top` experts with the largest logits (ties to the lower
+    index) as int32 [tokens, top], largest first, and the softmax over the chosen logits as float32 [tokens, top]."""
+    _cuda(x, router)
+    _columns(x, "x")
+    if router.dim() != 2 or not router.is_contiguous() or router.dtype != x.dtype or router.shape[1] != x.shape[1]:
+        raise KernelError(f"router_topk: the router {tuple(router.shape)} {router.dtype} does not fit rows {tuple(x.shape)} {x.dtype}")
+    tokens, experts = x.shape[0], router.shape[0]
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_router_topk(_p(x), x.stride(0), _p(router), _code(x.dtype), _p(chosen), _p(weights), tokens, x.shape[1], experts,
+                                 top, _stream()))
+    return chosen, weights
+
+
+class RoutePlan:
+    """The (token, choice) entries of a step grouped by expert: `sorted` [entries] entry ids (token * top + choice) by expert
+    and in ascending order within one, `offsets` [experts + 1], and the tiles of rows a grouped product's blocks own."""
+
+    def __init__(self, chosen: torch.Tensor, experts: int):
+        lib = routed_experts_library()
+        self.entries = chosen.numel()
+        self.top = chosen.shape[1]
+        self.experts = experts
+        self.max_tiles = lib.mb_route_max_tiles(self.entries, experts)
+        ints = torch.empty((experts + 1 + self.entries + 2 * self.max_tiles,), dtype=torch.int32, device=chosen.device)
+        self.offsets = ints[:experts + 1]
+        self.sorted = ints[experts + 1:experts + 1 + self.entries]
+        self.tile_expert = ints[experts + 1 + self.entries:experts + 1 + self.entries + self.max_tiles]
+        self.tile_row = ints[experts + 1 + self.entries + self.max_tiles:]
+        _run(lib, lib.mb_route_sort(_p(chosen), self.entries, experts, _p(self.offsets), _p(self.sorted), _p(self.tile_expert),
+                                    _p(self.tile_row), self.max_tiles, _stream()))
+
+
+def route_sort(chosen: torch.Tensor, experts: int) -> RoutePlan:
+    _cuda(chosen)
+    _int32(chosen, "chosen")
+    if chosen.dim() != 2:
+        raise KernelError("route_sort: chosen must be [tokens, top]")
+    return RoutePlan(chosen, experts)
+
+
+def _expert_weights(w: torch.Tensor, experts: int, name: str):
+    if w.dim() != 3 or w.shape[0] != experts or not w.is_contiguous():
+        raise KernelError(f"{name}: expert matrices must be contiguous [{experts}, n, k], got {tuple(w.shape)}")
+
+
+def expert_first_product(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, plan: RoutePlan, limit: float, slope: float,
+                         tensor_cores: bool = True) -> torch.Tensor:
+    """mid [entries, n] (rows in the plan's sorted order, x's dtype): for every entry of expert e and its token's row x,
+    g = min(gate_w[e] . x, limit), u = clamp(up_w[e] . x, -limit, limit), mid = g * sigmoid(slope * g) * (u + 1)."""
+    _cuda(x, gate_w, up_w)
+    _columns(x, "x")
+    _expert_weights(gate_w, plan.experts, "expert_first_product")
+    _expert_weights(up_w, plan.experts, "expert_first_product")
+    if gate_w.shape != up_w.shape or gate_w.shape[2] != x.shape[1] or not (gate_w.dtype == up_w.dtype == x.dtype):
+        raise KernelError(f"expert_first_product: matrices {tuple(gate_w.shape)} / {tuple(up_w.shape)} do not fit rows {tuple(x.shape)}")
+    n, k = gate_w.shape[1], gate_w.shape[2]
+    mid = torch.empty((plan.entries, n), dtype=x.dtype, device=x.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_expert_product(_p(x), x.stride(0), _p(gate_w), _p(up_w), _p(mid), None, n, _code(x.dtype), _p(plan.sorted),
+                                    _p(plan.offsets), _p(plan.tile_expert), _p(plan.tile_row), plan.max_tiles, plan.top, n, k,
+                                    ctypes.c_float(limit), ctypes.c_float(slope), 1, 1 if tensor_cores else 0, _stream()))
+    return mid
+
+
+def expert_second_product(mid: torch.Tensor, down_w: torch.Tensor, plan: RoutePlan, tensor_cores: bool = True) -> torch.Tensor:
+    """slot_out float32 [entries, n], row token * top + choice: down_w[e] . mid row of that entry (float32 sums)."""
+    _cuda(mid, down_w)
+    _expert_weights(down_w, plan.experts, "expert_second_product")
+    if mid.dim() != 2 or not mid.is_contiguous() or mid.shape[0] != plan.entries or down_w.shape[2] != mid.shape[1] or down_w.dtype != mid.dtype:
+        raise KernelError(f"expert_second_product: matrices {tuple(down_w.shape)} do not fit rows {tuple(mid.shape)}")
+    n, k = down_w.shape[1], down_w.shape[2]
+    slot_out = torch.empty((plan.entries, n), dtype=torch.float32, device=mid.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_expert_product(_p(mid), mid.stride(0), _p(down_w), None, None, _p(slot_out), n, _code(mid.dtype), _p(plan.sorted),
+                                    _p(plan.offsets), _p(plan.tile_expert), _p(plan.tile_row), plan.max_tiles, plan.top, n, k,
+                                    ctypes.c_float(0.0), ctypes.c_float(0.0), 0, 1 if tensor_cores else 0, _stream()))
+    return slot_out
+
+
+def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> None:
+    """out = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and up column
+    slices of one tensor."""
+    _cuda(gate, up, out)
+    for name, t in (("gate", gate), ("up", up), ("out", out)):
+        _columns(t, name)
+    if gate.shape != up.shape or out.shape != gate.shape or gate.stride(0) != up.stride(0) or not (gate.dtype == up.dtype == out.dtype):
+        raise KernelError("clamped_swish: gate, up and out must share shape and dtype, gate and up one row stride")
+    lib = routed_experts_library()
+    _run(lib, lib.mb_clamped_swish(_p(gate), _p(up), gate.stride(0), _p(out), out.stride(0), _code(gate.dtype), gate.shape[0],
+                                   gate.shape[1], ctypes.c_float(limit), ctypes.c_float(slope), _stream()))
+
+
+def expert_combine(slot_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                   score: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_s weights[t, s] * slot_out[t * top + s] (+ sigmoid(score[t]) * shared[t]) as float32 [tokens, width];
+    shared float32 [tokens, width], score one number per token ([tokens, 1], may be a column slice)."""
+    _cuda(slot_out, weights, shared, score)
+    tokens, top = weights.shape
+    width = slot_out.shape[1]
+    if slot_out.dtype != torch.float32 or not slot_out.is_contiguous() or slot_out.shape[0] != tokens * top \
+            or weights.dtype != torch.float32 or not weights.is_contiguous():
+        raise KernelError("expert_combine: slot_out float32 [tokens * top, width] and weights float32 [tokens, top] are needed")
+    if (shared is None) != (score is None):
+        raise KernelError("expert_combine: a shared expert and its gate scores come together")
+    if shared is not None:
+        _columns(score, "score")
+        if shared.dtype != torch.float32 or not shared.is_contiguous() or tuple(shared.shape) != (tokens, width) or score.shape[0] != tokens:
+            raise KernelError("expert_combine: shared must be contiguous float32 [tokens, width] with one score per token")
+    out = torch.empty((tokens, width), dtype=torch.float32, device=slot_out.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_expert_combine(_p(slot_out), _p(weights), _p(shared), _p(score), score.stride(0) if score is not None else 0,
+                                    _code(score.dtype) if score is not None else _F32, _p(out), tokens, width, top, _stream()))
     return out

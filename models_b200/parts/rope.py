@@ -8,6 +8,11 @@ scaling fills the reference's per-pair divisors: pairs whose wavelength 2*pi/fre
 original/high are untouched, above original/low are divided by `factor`, and in between
 freq' = (1-s)*freq/factor + s*freq with s = (original/wavelength - low)/(high - low).
 
+"yarn" scaling replaces the frequencies themselves (worked out in double, rounded to float): with
+pair(t) = dims * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(pair(high)), 0), hi = min(ceil(pair(low)),
+dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), freq'_i = freq_i / factor * ramp_i +
+freq_i * (1 - ramp_i).  A scaling's `magnitude` multiplies every cosine and sine.
+
 The rotation itself runs inside the mixer's cache-write kernel, which reads these tables.
 """
 
@@ -30,8 +35,10 @@ def pair_frequencies(rotary_dim: int, theta: float) -> torch.Tensor:
 def pair_divisors(frequencies: torch.Tensor, scaling) -> torch.Tensor | None:
     if scaling is None or scaling.kind == "linear":
         return None
+    if scaling.kind == "yarn":
+        return None  # the frequencies themselves are replaced: `stretched_frequencies`
     if scaling.kind != "llama3":
-        raise ValueError(f"rope scaling {scaling.kind!r} is not built (known: linear, llama3)")
+        raise ValueError(f"rope scaling {scaling.kind!r} is not built (known: linear, llama3, yarn)")
     low_wavelength = scaling.original_max_position / scaling.low_freq_factor
     high_wavelength = scaling.original_max_position / scaling.high_freq_factor
     divisors = []
@@ -48,6 +55,21 @@ def pair_divisors(frequencies: torch.Tensor, scaling) -> torch.Tensor | None:
     return torch.tensor(divisors, dtype=torch.float64).to(torch.float32)
 
 
+def stretched_frequencies(rotary_dim: int, theta: float, scaling) -> torch.Tensor:
+    """The pair frequencies under "yarn" scaling, in double and then rounded to float."""
+    def pair_of(turns: float) -> float:
+        return rotary_dim * math.log(scaling.original_max_position / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_of(scaling.high_freq_factor)), 0)
+    hi = min(math.ceil(pair_of(scaling.low_freq_factor)), rotary_dim - 1)
+    out = []
+    for i in range(rotary_dim // 2):
+        f = 1.0 / math.pow(theta, (2.0 * i) / rotary_dim)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / scaling.factor * ramp + f * (1.0 - ramp))
+    return torch.tensor(out, dtype=torch.float64).to(torch.float32)
+
+
 class RotaryEmbedding(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -57,7 +79,10 @@ class RotaryEmbedding(Part):
             raise ValueError(f"rope pairing must be 'half' or 'interleaved', got {spec.pairing!r}")
         self.rotary_dim = spec.rotary_dim
         self.interleaved = spec.pairing == "interleaved"
-        frequencies = pair_frequencies(spec.rotary_dim, spec.theta)
+        if spec.scaling is not None and spec.scaling.kind == "yarn":
+            frequencies = stretched_frequencies(spec.rotary_dim, spec.theta, spec.scaling)
+        else:
+            frequencies = pair_frequencies(spec.rotary_dim, spec.theta)
         divisors = pair_divisors(frequencies, spec.scaling)
         scale = 1.0
         if spec.scaling is not None and spec.scaling.kind == "linear":
@@ -68,8 +93,9 @@ class RotaryEmbedding(Part):
         if divisors is not None:
             angle = angle / divisors[None, :]
         angle = angle.to(torch.float64)
-        self.cos = torch.cos(angle).to(torch.float32).contiguous().to(runtime.device)
-        self.sin = torch.sin(angle).to(torch.float32).contiguous().to(runtime.device)
+        magnitude = float(spec.scaling.magnitude) if spec.scaling is not None else 1.0
+        self.cos = (torch.cos(angle) * magnitude).to(torch.float32).contiguous().to(runtime.device)
+        self.sin = (torch.sin(angle) * magnitude).to(torch.float32).contiguous().to(runtime.device)
 
 
 register_part("position", "rope", RotaryEmbedding)
