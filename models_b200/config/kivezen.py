@@ -71,7 +71,7 @@ MAGNITUDE_SLOPE = 0.1  # stretched rotary tables are multiplied by 0.1 * ln(fact
 @dataclass(frozen=True)
 class KivezenScaling:
     factor: float
-    original: int
+    original: float  # positions the unstretched frequencies were made for
     fast: float
     slow: float
 
@@ -144,7 +144,7 @@ def _attention(mixer, where: str) -> KivezenAttention:
         s = rot.get("scaling")
         if s is not None:
             sw = where + ".rot.scaling"
-            scaling = KivezenScaling(_float(s, "factor", sw, positive=True), _int(s, "original", sw),
+            scaling = KivezenScaling(_float(s, "factor", sw, positive=True), _float(s, "original", sw, positive=True),
                                      _float(s, "fast", sw, positive=True), _float(s, "slow", sw, positive=True))
     return KivezenAttention(heads, kv_heads, dim, vdim, _float(mixer, "scale", where), softcap, dims, base, scaling)
 
@@ -315,6 +315,10 @@ class KivezenConfig:
                         hc[f"{which}_{r}"] = f"{p}{q}.{r}"
             blocks.append(HyperBlockSpec(mixer=mixer, feed_forward=feed_forward, mixer_norm=NormSpec(W, eps, {"weight": p + "norm1"}),
                                          feed_forward_norm=feed_forward_norm, streams=self.streams, weights=hc))
+        # a layer without a feed-forward reads no second norm and no second set of connections; a file that holds them all
+        # the same is taken
+        unused = tuple(pattern for i, layer in enumerate(self.layers) if layer.mlp is None
+                       for pattern in (f"l{i}.norm2", f"l{i}.hc2.*"))
         return ModelSpec(
             architecture=self.architecture,
             vocab_size=self.vocab,
@@ -326,4 +330,5 @@ class KivezenConfig:
             final_norm=NormSpec(W, eps, {"weight": "final.norm"}),
             head=HeadSpec(self.vocab, W, False, {"weight": "head"}, softcap=self.logit_softcap),
             residual_streams=max(1, self.streams),
+            ignored_tensors=unused,
         )
