@@ -162,9 +162,20 @@ def route(h, router, top):
     return chosen, torch.softmax(logits, dim=-1)
 
 
-def routed_feed_forward(h, w, prefix, mlp):
+def route_margin(h, router, top):
+    """Per token, how far the last chosen logit lies above the first one left out, in units of the logits' root mean
+    square (infinite when every expert is chosen): a small number is a close call that roundings may turn."""
+    z = torch.sort(h @ router.to(F).T, dim=-1, descending=True).values
+    if top >= z.shape[1]:
+        return torch.full((z.shape[0],), math.inf, dtype=F)
+    return (z[:, top - 1] - z[:, top]) / torch.sqrt(torch.mean(z ** 2, dim=-1))
+
+
+def routed_feed_forward(h, w, prefix, mlp, margins=None):
     n, top = mlp["router"]["experts"], mlp["router"]["top"]
     chosen, weights = route(h, w[prefix + "router"], top)
+    if margins is not None:
+        margins.append(route_margin(h, w[prefix + "router"], top))
     out = torch.zeros(h.shape[0], w[prefix + "e0.down"].shape[0], dtype=F)
     for e in range(n):
         rows, slot = (chosen == e).nonzero(as_tuple=True)
@@ -177,8 +188,8 @@ def routed_feed_forward(h, w, prefix, mlp):
     return out
 
 
-def feed_forward(h, w, prefix, mlp):
-    return dense_feed_forward(h, w, prefix) if mlp["kind"] == "dense" else routed_feed_forward(h, w, prefix, mlp)
+def feed_forward(h, w, prefix, mlp, margins=None):
+    return dense_feed_forward(h, w, prefix) if mlp["kind"] == "dense" else routed_feed_forward(h, w, prefix, mlp, margins)
 
 
 def schedule(config):
@@ -203,9 +214,9 @@ def sublayer(streams, w, layer_prefix, which, eps, hyper, function):
     return torch.einsum("sr,std->rtd", w[hc + "mix"].to(F), streams) + w[hc + "out"].to(F)[:, None, None] * y[None]
 
 
-def forward(config, w, tokens, observe=None, angle_dtype=F):
+def forward(config, w, tokens, observe=None, angle_dtype=F, margins=None):
     """tokens: a list of ids -> logits [T, vocab] (float64).  `observe(run, x)` gets the sum of the streams after
-    every run of a layer."""
+    every run of a layer; `margins` (a list) gets, for every run of a mixture of experts, each token's `route_margin`."""
     eps = float(config["norm"]["eps"])
     hyper = "streams" in config
     S = int(config.get("streams", 1))
@@ -219,7 +230,7 @@ def forward(config, w, tokens, observe=None, angle_dtype=F):
             mixer = lambda h: lightning_mixer(h, w, p + "mix.", layer["mixer"], eps)  # noqa: E731
         streams = sublayer(streams, w, p, 1, eps, hyper, mixer)
         if layer.get("mlp") is not None:
-            streams = sublayer(streams, w, p, 2, eps, hyper, lambda h: feed_forward(h, w, p + "mlp.", layer["mlp"]))
+            streams = sublayer(streams, w, p, 2, eps, hyper, lambda h: feed_forward(h, w, p + "mlp.", layer["mlp"], margins))
         if observe is not None:
             observe(run, streams.sum(0))
     x = rms_norm(streams.sum(0), w["final.norm"].to(F), eps)

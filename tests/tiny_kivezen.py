@@ -98,7 +98,7 @@ def make_folder(raw: dict, seed: int, root, std: float = 0.15) -> Path:
             if kind == "mix":
                 t = torch.eye(S) * 0.7 + (torch.rand(S, S, generator=g) - 0.3) * 0.5
             elif kind == "in":
-                t = (torch.rand(S, generator=g) + 0.3) * (1.0 if S == 1 else torch.tensor([1.0, -0.6, 0.8][:S]))
+                t = (torch.rand(S, generator=g) + 0.3) * (1.0 if S == 1 else torch.tensor([(1.0, -0.6, 0.8, 0.5)[i % 4] for i in range(S)]))
             else:
                 t = torch.rand(S, generator=g) + 0.5
             weights[name] = t.to(torch.bfloat16)
@@ -108,7 +108,22 @@ def make_folder(raw: dict, seed: int, root, std: float = 0.15) -> Path:
     return folder
 
 
-def plain_logits(folder, tokens, hidden_out=None) -> torch.Tensor:
+def plain_logits(folder, tokens, hidden_out=None, margins=None) -> torch.Tensor:
     config, weights = plain_kivezen.read_model_folder(folder)
     observe = None if hidden_out is None else (lambda run, x: hidden_out.append(x.clone()))
-    return plain_kivezen.forward(config, weights, list(tokens), observe)
+    return plain_kivezen.forward(config, weights, list(tokens), observe, margins=margins)
+
+
+CLOSE_CALL = 0.05  # of the router logits' root mean square
+
+
+def plain_logits_and_sure(folder, tokens):
+    """The logits, and per position whether every router decision of that token and of all tokens before it was clear of
+    a close call: in bfloat16 the roundings of the router's input may turn a close one; that token then runs through
+    another expert, and every later token reads it through the cache and the recurrent state."""
+    margins = []
+    logits = plain_logits(folder, tokens, margins=margins)
+    sure = torch.ones(len(tokens), dtype=torch.bool)
+    for m in margins:
+        sure &= m >= CLOSE_CALL
+    return logits, torch.cumprod(sure.to(torch.int64), dim=0).bool()
