@@ -590,21 +590,205 @@ def lovurax_kernels(z, peak, prompt=2048, batch=8, context=1536):
     return out
 
 
+# --design kivezen: the Kivezen decoder (capped attention with a sink and rotated values, lightning layers, routed
+# experts, several residual streams) beside a Lovurax of equal size: the model of this package whose layers are nearest
+# (attention over the same paged kernels, a retention walk); equal size counts the parameters a token uses.
+
+KIVEZEN_SIZES = {
+    # width, layers (KIVEZEN_ORDER in turn), heads, key/value heads, key size, value size, dense ff, experts, chosen per token,
+    # an expert's ff, the shared expert's ff, residual streams; `rank` only sizes the Lovurax beside it
+    "s": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=64, vdim=128, ff=2048, experts=16, top=2, expert_ff=512, shared_ff=512,
+              streams=2, rank=256),
+    "m": dict(width=2048, layers=16, heads=16, kv_heads=4, dim=64, vdim=128, ff=4096, experts=32, top=4, expert_ff=512, shared_ff=1024,
+              streams=4, rank=256),
+}
+KIVEZEN_ORDER = (("lightning", "dense"), ("attention", "moe"), ("attention", "dense"), ("lightning", "moe"))
+
+
+def kivezen_config(z):
+    H, D, DV = z["heads"], z["dim"], z["vdim"]
+    mixers = {
+        "attention": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": DV, "scale": D ** -0.5, "softcap": 50.0,
+                      "rot": {"dims": D // 2, "base": 500000.0,
+                              "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "lightning": {"heads": H, "dim": D, "vdim": DV, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)]},
+    }
+    mlps = {"dense": {"kind": "dense", "ff": z["ff"]},
+            "moe": {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"], "limit": 7.0},
+                    "shared": {"ff": z["shared_ff"], "limit": 7.0}}}
+    layers = []
+    for i in range(z["layers"]):
+        mixer, mlp = KIVEZEN_ORDER[i % 4]
+        layers.append({"type": mixer, "mixer": mixers[mixer], "mlp": mlps[mlp]})
+    return {"architecture": "Kivezen", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "streams": z["streams"],
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def kivezen_layer_params(z):
+    """Matrix parameters a token uses in a layer (of the experts only the chosen ones and the shared one), averaged over
+    the four layers of a turn."""
+    w, h, g, d, dv = (z[k] for k in ("width", "heads", "kv_heads", "dim", "vdim"))
+    mixer = {"attention": w * (h * d + g * d + g * dv) + h * dv * w, "lightning": w * (2 * h * d + 2 * h * dv) + h * dv * w}
+    mlp = {"dense": 2 * w * z["ff"], "moe": z["top"] * 3 * w * z["expert_ff"] + 3 * w * z["shared_ff"] + w * (z["experts"] + 1)}
+    return sum(mixer[a] + mlp[b] for a, b in KIVEZEN_ORDER) // 4
+
+
+def lovurax_of_equal_size(z):
+    """A Lovurax of the same width, layers, heads and head sizes whose feed-forward width (a multiple of 256) makes a
+    layer's parameters equal to those a Kivezen token uses."""
+    w = z["width"]
+    ff = max(256, round((kivezen_layer_params(z) - lovurax_layer_params(dict(z, ff=0))) / (2 * w) / 256) * 256)
+    return lovurax_config(dict(z, ff=ff))
+
+
+def kivezen_kernels(z, peak, prompt=2048, batch=8, context=1536):
+    """The design's kernels alone beside the like kernels of the other models at equal sizes, each with its fraction of
+    the measured peak that bounds it."""
+    import torch
+
+    from models_b200.kernels import ops
+    from models_b200.parts.linear import linear
+
+    dev, bf = "cuda", torch.bfloat16
+    H, G, D, DV, W = (z[k] for k in ("heads", "kv_heads", "dim", "vdim", "width"))
+    E, top, F, S = z["experts"], z["top"], z["expert_ff"], z["streams"]
+    page = 64
+    out = {}
+
+    def paged(sequences, length, key, value):
+        pages = sequences * (-(-length // page))
+        k_pool = torch.randn((pages + 1, G, page, key), device=dev).to(bf)
+        v_pool = torch.randn((pages + 1, G, page, value), device=dev).to(bf)
+        table = (torch.arange(pages, dtype=torch.int32, device=dev) + 1).reshape(sequences, -1).contiguous()
+        return k_pool, v_pool, table
+
+    def rated(us, flops=None, moved=None):
+        if flops is not None:
+            return {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak["bf16_tflops"]}
+        return {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+
+    longest = max(prompt, context)
+    angle = torch.arange(longest, dtype=torch.float32, device=dev)[:, None]
+    cos, sin = (f(angle * torch.rand((1, D // 4), device=dev)).contiguous() for f in (torch.cos, torch.sin))  # D / 2 coordinates turn
+    vcos, vsin = (f(angle * torch.rand((1, DV // 2), device=dev)).contiguous() for f in (torch.cos, torch.sin))
+    temperature = torch.rand(H, device=dev) + 0.5
+    for name, rows, cu_q, lengths, q_len in (("prompt", prompt, [0, prompt], [prompt], prompt),
+                                             ("decode", batch, list(range(batch + 1)), [context] * batch, 1)):
+        sequences = len(lengths)
+        cu = torch.tensor(cu_q, dtype=torch.int32, device=dev)
+        kv = torch.tensor(lengths, dtype=torch.int32, device=dev)
+        pairs = sum(sum(range(n - q_len + 1, n + 1)) for n in lengths)  # (query, key) pairs of a head
+        positions = torch.cat([torch.arange(n - q_len, n) for n in lengths]).to(torch.int32).to(dev)
+        # capped attention (a temperature per head, the cap, the sink, the turn back) beside the sigmoid attention of Lovurax
+        k_pool, v_pool, table = paged(sequences, lengths[0], D, DV)
+        q, o = torch.randn((rows, H * D), device=dev).to(bf), torch.empty((rows, H * DV), dtype=bf, device=dev)
+        us = time_kernel(lambda: ops.gated_attention(q, o, k_pool, v_pool, table, cu, kv, q_len, H, G, D, DV, "softmax", D ** -0.5,
+                                                     head_scale=temperature, softcap=50.0, sink=True, turn_cos=vcos, turn_sin=vsin))
+        out[f"{name}_capped_attention"] = rated(us, flops=pairs * H * (2 * D + 2 * DV)) if q_len > 1 else \
+            rated(us, moved=sum(lengths) * G * (D + DV) * 2)
+        gate, bias = torch.randn((rows, H * DV), device=dev).to(bf), torch.zeros(H, device=dev)
+        us = time_kernel(lambda: ops.gated_attention(q, o, k_pool, v_pool, table, cu, kv, q_len, H, G, D, DV, "sigmoid", D ** -0.5, 8.0,
+                                                     bias, gate, "element"))
+        out[f"{name}_sigmoid_attention_lovurax"] = rated(us, flops=pairs * H * (2 * D + 2 * DV)) if q_len > 1 else \
+            rated(us, moved=sum(lengths) * G * (D + DV) * 2)
+        # what stands before it: rotation, unit norm, rotated values, the pools; beside Lovurax's norm and store
+        qkv = torch.randn((rows, (H + G) * D + G * DV), device=dev).to(bf)
+        a, b = H * D, (H + G) * D
+        mapping = (torch.arange(rows, dtype=torch.int32, device=dev) + page)
+        moved = rows * (2 * H * D + 2 * G * D + 2 * G * DV) * 2
+        us = time_kernel(lambda: ops.rotate_norm_store(qkv[:, :a], qkv[:, a:b], qkv[:, b:], positions, cos, sin, D // 2, True, True, 1e-6,
+                                                       vcos, vsin, DV, k_pool, v_pool, mapping, H, G, D, DV))
+        out[f"{name}_rotate_norm_store"] = rated(us, moved=moved)
+        us = time_kernel(lambda: ops.norm_store(qkv[:, :a], qkv[:, a:b], qkv[:, b:], positions, None, None, 1e-6, 0.4, 128, k_pool, v_pool,
+                                                mapping, H, G, D, DV))
+        out[f"{name}_norm_store_lovurax"] = rated(us, moved=moved)
+        # lightning (silu on the way in, no rotation, floats out, one norm over all heads and a sigmoid gate in a second
+        # kernel) beside the retention of Lovurax (rotation, a norm per head and a silu gate in the walk)
+        state = torch.zeros((sequences + 1, H, D, DV), dtype=torch.float32, device=dev)
+        proj = torch.randn((rows, 2 * H * D + 2 * H * DV), device=dev).to(bf)
+        a, b, c = H * D, 2 * H * D, 2 * H * D + H * DV
+        y = torch.empty((rows, H * DV), dtype=bf, device=dev)
+        raw = torch.empty((rows, H * DV), dtype=torch.float32, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        gain = torch.ones(H * DV, device=dev)
+        slots = torch.arange(sequences, dtype=torch.int32, device=dev)
+        moved = rows * (2 * H * D + 3 * H * DV) * 2 + sequences * H * D * DV * 8
+        us = time_kernel(lambda: (ops.retention_scan(proj[:, :a], proj[:, a:b], proj[:, b:c], None, positions, None, None, 0, decay, 1.0, 1e-6,
+                                                     state, slots, cu, H, D, DV, None, 1.0, q_len, input_activation="silu", raw_out=raw),
+                                  ops.group_norm_gate(raw, gain, proj[:, c:], y, 1e-6, "sigmoid")))
+        out[f"{name}_lightning"] = dict(rated(us, moved=moved + rows * H * DV * 8), fp32_tflops=rows * H * 4 * D * DV / us / 1e6)
+        tables = torch.rand((longest, D // 4), device=dev)
+        us = time_kernel(lambda: ops.retention_scan(proj[:, :a], proj[:, a:b], proj[:, b:c], proj[:, c:], positions, tables, tables, D // 2,
+                                                    decay, D ** -0.5, 1e-6, state, slots, cu, H, D, DV, y, 1.0, q_len))
+        out[f"{name}_retention_lovurax"] = dict(rated(us, moved=moved), fp32_tflops=rows * H * 4 * D * DV / us / 1e6)
+        # routed experts (router, sorting, the two grouped products, the weighted sum) beside a dense gated feed-forward whose
+        # width is what a token uses (top experts side by side), through the products the package gives a dense layer
+        x = torch.randn((rows, W), device=dev).to(bf)
+        router = (torch.randn((E, W), device=dev) * 0.02).to(bf)
+        w_gate, w_up = ((torch.randn((E, F, W), device=dev) * 0.02).to(bf) for _ in range(2))
+        w_down = (torch.randn((E, W, F), device=dev) * 0.02).to(bf)
+
+        def routed():  # (as the model's feed-forward runs them)
+            chosen, weights = ops.router_topk(x, router, top)
+            if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
+                mid = ops.expert_rows_first(x, w_gate, w_up, chosen, 7.0, 1.702)
+                return ops.expert_combine(ops.expert_rows_second(mid, w_down, chosen), weights)
+            plan = ops.route_sort(chosen, E)
+            mid = ops.expert_first_product(x, w_gate, w_up, plan, 7.0, 1.702)
+            return ops.expert_combine(ops.expert_second_product(mid, w_down, plan), weights)
+
+        us = time_kernel(routed)
+        flops = rows * top * 6 * W * F
+        touched = min(E, rows * top)  # (about: experts whose matrices a small step reads)
+        out[f"{name}_routed_experts"] = rated(us, flops=flops) if q_len > 1 else rated(us, moved=touched * 3 * W * F * 2)
+        dense_in = (torch.randn((2 * top * F, W), device=dev) * 0.02).to(bf)
+        dense_out = (torch.randn((W, top * F), device=dev) * 0.02).to(bf)
+        dense_mid = torch.empty((rows, top * F), dtype=bf, device=dev)
+
+        def dense():
+            both = linear(x, dense_in, bf)
+            ops.clamped_swish(both[:, :top * F], both[:, top * F:], dense_mid, 7.0, 1.702)
+            return linear(dense_mid, dense_out, torch.float32)
+
+        us = time_kernel(dense)
+        out[f"{name}_dense_of_equal_use"] = rated(us, flops=flops) if q_len > 1 else rated(us, moved=top * 3 * W * F * 2)
+        # the residual streams: reading (weighted sum and norm) and writing (mixing and addition) beside the one-stream kernels
+        streams = torch.randn((rows, S * W), device=dev)
+        delta = torch.randn((rows, W), device=dev)
+        read, write, mix = torch.rand(S, device=dev), torch.rand(S, device=dev), torch.rand((S, S), device=dev)
+        ones = torch.ones(W, device=dev)
+        us = time_kernel(lambda: ops.hyper_read_norm(streams, read, ones, 1e-6, bf))
+        out[f"{name}_streams_read_norm"] = rated(us, moved=rows * W * (4 * S + 2))
+        us = time_kernel(lambda: ops.hyper_write(streams, delta, write, mix))
+        out[f"{name}_streams_write"] = rated(us, moved=rows * W * (8 * S + 4))
+        one = torch.randn((rows, W), device=dev)
+        us = time_kernel(lambda: ops.add_rmsnorm(one, None, ones, 1e-6, bf))
+        out[f"{name}_rmsnorm_llama"] = rated(us, moved=rows * W * 6)
+        us = time_kernel(lambda: ops.residual_add(one, delta))
+        out[f"{name}_residual_add_llama"] = rated(us, moved=rows * W * 12)
+    return out
+
+
 def design_run(args) -> int:
     import torch
 
     peak = peaks()
     batch, prompt, prefill_tokens, steps, warmup = 8, 512, 2048, args.steps or 64, max(args.warmup, 3)
+    other, other_title = "llama", "LlamaForCausalLM of equal size"
     if args.design == "kabanex":
         title, all_sizes, make, params, beside, alone = "Kabanex", DESIGN_SIZES, kabanex_config, kabanex_layer_params, \
             (lambda z: llama_like(z)), design_kernels
+    elif args.design == "kivezen":
+        title, all_sizes, make, params, beside, alone = "Kivezen", KIVEZEN_SIZES, kivezen_config, kivezen_layer_params, \
+            lovurax_of_equal_size, kivezen_kernels
+        other, other_title = "lovurax", "Lovurax of equal size (the parameters a token uses)"
     else:
         title, all_sizes, make, params, beside, alone = "Lovurax", LOVURAX_SIZES, lovurax_config, lovurax_layer_params, \
             (lambda z: llama_of_equal_size(z, lovurax_layer_params(z))), lovurax_kernels
     sizes = {}
     for name, z in all_sizes.items():
         entry = {"sizes": z, "layer_params": params(z)}
-        for arch, config in ((args.design, make(z)), ("llama", beside(z))):
+        for arch, config in ((args.design, make(z)), (other, beside(z))):
             model = make_model(config, batch, prefill_tokens + 64)
             ms = device_prefill(model, prefill_tokens)
             run = device_decode(model, batch, steps, warmup, prompt=prompt)
@@ -613,12 +797,14 @@ def design_run(args) -> int:
                            "launches_per_step": run["launches"] / steps, "kernels": run["kernels"]}
             if arch == "llama":
                 entry[arch]["intermediate_size"] = config["intermediate_size"]
+            elif arch == other:
+                entry[arch]["ff"] = config["layers"][0]["mlp"]["ff"]
             model.close()
             del model
             torch.cuda.empty_cache()
         entry["kernels_alone"] = alone(z, peak)
         sizes[name] = entry
-    print(json.dumps({"design": title, "beside": "LlamaForCausalLM of equal size", "dtype": "bf16", "gpu": torch.cuda.get_device_name(0),
+    print(json.dumps({"design": title, "beside": other_title, "dtype": "bf16", "gpu": torch.cuda.get_device_name(0),
                       "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
                       "workload": {"prefill_tokens": prefill_tokens, "decode_batch": batch, "decode_prompt": prompt, "decode_steps": steps,
                                    "warmup": warmup, "vocab": DESIGN_VOCAB},
@@ -641,8 +827,9 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the workload's prefill alone and print its figures (for profiling)")
-    parser.add_argument("--design", default=None, choices=["kabanex", "lovurax"],
-                        help="instead of the default run: this design beside a Llama of equal size (prefill, decode, its kernels alone)")
+    parser.add_argument("--design", default=None, choices=["kabanex", "lovurax", "kivezen"],
+                        help="instead of the default run: this design beside a model of equal size (a Llama; for kivezen a Lovurax): "
+                             "prefill, decode, its kernels alone")
     args = parser.parse_args()
     if args.design and args.impl == "ours":
         if args.gpus != 1:

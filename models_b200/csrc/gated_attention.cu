@@ -133,6 +133,90 @@ __global__ void rotate_norm_store_kernel(T* __restrict__ q, int q_stride, const 
     }
 }
 
+// Two neighbouring elements with one load or store.
+template <typename T>
+struct Two;
+template <>
+struct Two<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <>
+struct Two<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+    }
+};
+
+// The same for pairs (2i, 2i + 1) and even sizes: a lane holds whole pairs, one load and one store per pair, the pair's
+// partner never read a second time.  Rows and heads must start on even elements.
+template <typename T>
+__global__ void rotate_norm_store_pairs_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                                               const T* __restrict__ v, int v_stride, const int* __restrict__ positions, float eps,
+                                               Rotation rotation, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                               const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
+                                               int value_dim, int page_size) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    constexpr int kPer = 4;  // pairs per lane: heads of up to 256
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int pos = positions[token];
+    const int slot = slot_mapping[token];
+    const size_t page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+    const int turning = rotation.dim / 2, pairs = head_dim / 2;
+    const float* cos_row = turning > 0 ? rotation.cos + (size_t)pos * turning : nullptr;
+    const float* sin_row = turning > 0 ? rotation.sin + (size_t)pos * turning : nullptr;
+    for (int item = warp; item < heads + kv_heads; item += warps) {
+        const bool is_query = item < heads;
+        const int head = is_query ? item : item - heads;
+        if (!is_query && slot < 0) continue;  // a padding row stores nothing
+        T* q_head = q + (size_t)token * q_stride + (size_t)head * head_dim;
+        const T* src = is_query ? q_head : k + (size_t)token * k_stride + (size_t)head * head_dim;
+        T* dst = is_query ? q_head : k_pool + ((page * kv_heads + head) * page_size + offset) * head_dim;
+        float2 value[kPer];
+        float ssq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int p = lane + 32 * i;
+            value[i] = make_float2(0.0f, 0.0f);
+            if (p < pairs) {
+                const float2 x = Two<T>::load(src + 2 * p);
+                if (p < turning) {
+                    const float c = cos_row[p], sn = sin_row[p];
+                    value[i] = make_float2(x.x * c - x.y * sn, x.y * c + x.x * sn);
+                } else {
+                    value[i] = x;
+                }
+            }
+            ssq = fmaf(value[i].x, value[i].x, fmaf(value[i].y, value[i].y, ssq));
+        }
+        const float factor = rotation.unit ? 1.0f / sqrtf(warp_sum(ssq) / (float)head_dim + eps) : 1.0f;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int p = lane + 32 * i;
+            if (p < pairs) Two<T>::store(dst + 2 * p, value[i].x * factor, value[i].y * factor);
+        }
+    }
+    if (slot < 0 || value_dim <= 0) return;
+    const T* v_row = v + (size_t)token * v_stride;
+    const int value_turning = rotation.value_dim_rotated / 2, value_pairs = value_dim / 2;
+    const float* value_cos = value_turning > 0 ? rotation.value_cos + (size_t)pos * value_turning : nullptr;
+    const float* value_sin = value_turning > 0 ? rotation.value_sin + (size_t)pos * value_turning : nullptr;
+    for (int item = threadIdx.x; item < kv_heads * value_pairs; item += blockDim.x) {
+        const int head = item / value_pairs, p = item % value_pairs;
+        float2 x = Two<T>::load(v_row + (size_t)head * value_dim + 2 * p);
+        if (p < value_turning) {
+            const float c = value_cos[p], sn = value_sin[p];
+            x = make_float2(x.x * c - x.y * sn, x.y * c + x.x * sn);
+        }
+        Two<T>::store(v_pool + ((page * kv_heads + head) * page_size + offset) * value_dim + 2 * p, x.x, x.y);
+    }
+}
+
 template <typename T>
 __global__ void norm_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
                                   const T* __restrict__ v, int v_stride, const int* __restrict__ positions,
@@ -705,6 +789,16 @@ int launch_rotate_norm_store(void* q, int q_stride, const void* k, int k_stride,
                              float eps, Rotation rotation, void* k_pool, void* v_pool, const int* slot_mapping, int tokens, int heads,
                              int kv_heads, int head_dim, int value_dim, int page_size, cudaStream_t stream) {
     const int warps = heads + kv_heads < 4 ? 4 : (heads + kv_heads > 16 ? 16 : heads + kv_heads);
+    const bool turns = rotation.dim > 0 || rotation.value_dim_rotated > 0;
+    const uintptr_t two = 2 * sizeof(T);
+    if ((rotation.interleaved || !turns) && head_dim % 2 == 0 && value_dim % 2 == 0 && q_stride % 2 == 0 && k_stride % 2 == 0 &&
+        v_stride % 2 == 0 && !((uintptr_t)q % two) && !((uintptr_t)k % two) && !((uintptr_t)v % two) && !((uintptr_t)k_pool % two) &&
+        !((uintptr_t)v_pool % two)) {
+        MB_LAUNCH("rotate_norm_store", rotate_norm_store_pairs_kernel<T>, dim3(tokens), dim3(32 * warps), 0, stream, true, (T*)q, q_stride,
+                  (const T*)k, k_stride, (const T*)v, v_stride, positions, eps, rotation, (T*)k_pool, (T*)v_pool, slot_mapping, heads,
+                  kv_heads, head_dim, value_dim, page_size);
+        return 0;
+    }
     MB_LAUNCH("rotate_norm_store", rotate_norm_store_kernel<T>, dim3(tokens), dim3(32 * warps), 0, stream, true, (T*)q, q_stride,
               (const T*)k, k_stride, (const T*)v, v_stride, positions, eps, rotation, (T*)k_pool, (T*)v_pool, slot_mapping, heads,
               kv_heads, head_dim, value_dim, page_size);

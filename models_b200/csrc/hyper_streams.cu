@@ -37,13 +37,21 @@ __global__ void stream_sum_kernel(const float* __restrict__ x, float* __restrict
     out[i] = sum;
 }
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 // grid (rows); block 256; shared: width floats + 32.  `in` holds the streams' read coefficients on the device.
-template <typename T>
+// kQuads: width is a multiple of 4; a thread reads four columns of every stream with one 16-byte load each, all streams'
+// loads of a step in flight together.
+template <typename T, bool kQuads>
 __global__ void __launch_bounds__(256)
 hyper_read_norm_kernel(const float* __restrict__ x, const float* __restrict__ in, const float* __restrict__ gain,
                        T* __restrict__ out, int width, int streams, float eps) {
     grid_launch_dependents();
-    extern __shared__ float row_shared[];
+    extern __shared__ __align__(16) float row_shared[];
     float* scratch = row_shared + width;
     float coefficient[kMaxStreams];
 #pragma unroll
@@ -52,17 +60,46 @@ hyper_read_norm_kernel(const float* __restrict__ x, const float* __restrict__ in
     const size_t row = blockIdx.x;
     const float* mine = x + row * streams * width;
     float ssq = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float u = 0.0f;
+    if (kQuads) {
+        const int quads = width / 4;
+        for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+            float4 v[kMaxStreams];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
-            if (s < streams) u = fmaf(coefficient[s], mine[(size_t)s * width + c], u);
-        row_shared[c] = u;
-        ssq = fmaf(u, u, ssq);
+            for (int s = 0; s < kMaxStreams; ++s)
+                if (s < streams) v[s] = reinterpret_cast<const float4*>(mine + (size_t)s * width)[c];
+            float4 u = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int s = 0; s < kMaxStreams; ++s)
+                if (s < streams) {
+                    u.x = fmaf(coefficient[s], v[s].x, u.x);
+                    u.y = fmaf(coefficient[s], v[s].y, u.y);
+                    u.z = fmaf(coefficient[s], v[s].z, u.z);
+                    u.w = fmaf(coefficient[s], v[s].w, u.w);
+                }
+            reinterpret_cast<float4*>(row_shared)[c] = u;
+            ssq = fmaf(u.x, u.x, fmaf(u.y, u.y, fmaf(u.z, u.z, fmaf(u.w, u.w, ssq))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float u = 0.0f;
+#pragma unroll
+            for (int s = 0; s < kMaxStreams; ++s)
+                if (s < streams) u = fmaf(coefficient[s], mine[(size_t)s * width + c], u);
+            row_shared[c] = u;
+            ssq = fmaf(u, u, ssq);
+        }
     }
     const float total = block_sum(ssq, scratch);
     const float inverse = 1.0f / sqrtf(total / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) Num<T>::store(out + row * width + c, row_shared[c] * inverse * gain[c]);
+    if (kQuads) {
+        for (int c = threadIdx.x; c < width / 4; c += blockDim.x) {
+            const float4 u = reinterpret_cast<const float4*>(row_shared)[c];
+            const float4 g = reinterpret_cast<const float4*>(gain)[c];
+            store4(out + row * width + c * 4, u.x * inverse * g.x, u.y * inverse * g.y, u.z * inverse * g.z, u.w * inverse * g.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) Num<T>::store(out + row * width + c, row_shared[c] * inverse * gain[c]);
+    }
 }
 
 // grid (ceil(tokens * width / 256)); block 256.  `coefficients`: out [streams] then mix [streams][streams] on the device.
@@ -126,16 +163,21 @@ MB_EXPORT int mb_hyper_read_norm(const float* x, const float* in, const float* g
     if (width <= 0 || streams <= 0 || streams > kMaxStreams) return fail("hyper_read_norm: width %d, streams %d (at most %d)", width, streams, kMaxStreams);
     const size_t smem = ((size_t)width + 32) * sizeof(float);
     if (smem > 200 * 1024) return fail("hyper_read_norm: a row of %d floats exceeds a block's shared memory", width);
+    const bool quads = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)gain & 15) && !((uintptr_t)out & 15);
+#define MB_READ_NORM(T, QUADS)                                                                                                       \
+    do {                                                                                                                             \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_read_norm_kernel<T, QUADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        MB_LAUNCH("hyper_read_norm", (hyper_read_norm_kernel<T, QUADS>), dim3(tokens), dim3(256), smem, stream, true, x, in, gain, (T*)out, \
+                  width, streams, eps);                                                                                              \
+    } while (0)
     if (out_dtype == MB_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_read_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("hyper_read_norm", hyper_read_norm_kernel<float>, dim3(tokens), dim3(256), smem, stream, true, x, in, gain, (float*)out, width, streams, eps);
+        if (quads) MB_READ_NORM(float, true); else MB_READ_NORM(float, false);
     } else if (out_dtype == MB_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_read_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("hyper_read_norm", hyper_read_norm_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), smem, stream, true, x, in, gain,
-                  (__nv_bfloat16*)out, width, streams, eps);
+        if (quads) MB_READ_NORM(__nv_bfloat16, true); else MB_READ_NORM(__nv_bfloat16, false);
     } else {
         return fail("hyper_read_norm: unknown dtype code %d", out_dtype);
     }
+#undef MB_READ_NORM
     return 0;
 }
 

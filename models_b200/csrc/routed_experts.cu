@@ -214,6 +214,90 @@ expert_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict
     }
 }
 
+// Few entries (a decode step): no sorting and no tiles.  grid (ceil(N / 32), entries); block 256: the block's entry
+// (token = entry / top, expert = chosen[entry]) is staged as floats in shared memory; a warp owns 4 of the block's 32
+// columns, its lanes walk K in pieces of 8 elements (16-byte loads of the weights, 8 or 4 in flight per lane) and the sums
+// meet in a shuffle.  Memory-bound: every matrix row is read once per entry that uses its expert.
+// kFirst: a = x [tokens][K]; mid [entry][N] = clamped_swish(gate_e . x, up_e . x), rows in entry order.
+// else:   a = mid [entries][K] in entry order; slot_out [entry][N] (float) = down_e . mid.
+template <typename T, bool kFirst, bool kVector>
+__global__ void __launch_bounds__(256)
+expert_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0, const T* __restrict__ w1, T* __restrict__ mid,
+                   float* __restrict__ slot_out, int out_stride, const int* __restrict__ chosen, int top, int experts, int N, int K,
+                   float limit, float slope) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    constexpr int kCols = 4;
+    constexpr int kSets = kFirst ? 2 : 1;
+    extern __shared__ __align__(16) float rows_shared[];  // K floats
+    const int entry = blockIdx.y;
+    const int expert = chosen[entry];
+    if (expert < 0 || expert >= experts) return;  // (a router that chose nothing real: nothing is written)
+    const T* src = a + (size_t)(kFirst ? entry / top : entry) * a_stride;
+    if (kVector) {
+        for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+            float v[8];
+            load8(src + c * 8, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rows_shared[c * 8 + i] = v[i];
+        }
+    } else {
+        for (int c = threadIdx.x; c < K; c += blockDim.x) rows_shared[c] = Num<T>::load(src + c);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * 8 + warp) * kCols;
+    if (n0 >= N) return;
+    const T* w_e[kSets];
+    w_e[0] = w0 + (size_t)expert * N * K;
+    if (kFirst) w_e[kSets - 1] = w1 + (size_t)expert * N * K;
+    float acc[kSets][kCols];
+#pragma unroll
+    for (int s = 0; s < kSets; ++s)
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) acc[s][j] = 0.0f;
+    if (kVector) {
+        for (int c = lane; c < K / 8; c += 32) {
+            float w[kSets][kCols][8];
+#pragma unroll
+            for (int s = 0; s < kSets; ++s)
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) load8(w_e[s] + (size_t)min(n0 + j, N - 1) * K + c * 8, w[s][j]);
+            const float4 x0 = *reinterpret_cast<const float4*>(rows_shared + c * 8);
+            const float4 x1 = *reinterpret_cast<const float4*>(rows_shared + c * 8 + 4);
+            const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int s = 0; s < kSets; ++s)
+#pragma unroll
+                for (int j = 0; j < kCols; ++j)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[s][j] = fmaf(x[i], w[s][j][i], acc[s][j]);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float x = rows_shared[k];
+#pragma unroll
+            for (int s = 0; s < kSets; ++s)
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) acc[s][j] = fmaf(x, Num<T>::load(w_e[s] + (size_t)min(n0 + j, N - 1) * K + k), acc[s][j]);
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < kSets; ++s)
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) acc[s][j] = warp_sum(acc[s][j]);
+    if (lane != 0) return;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) {
+        const int n = n0 + j;
+        if (n >= N) break;
+        if (kFirst)
+            Num<T>::store(mid + (size_t)entry * out_stride + n, clamped_swish(acc[0][j], acc[kSets - 1][j], limit, slope));
+        else
+            slot_out[(size_t)entry * out_stride + n] = acc[0][j];
+    }
+}
+
 // The same on the tensor cores: bfloat16, K a multiple of 16, rows of a and of the weights starting on 16 bytes.
 // Block 128: warp w owns rows 16w .. 16w + 15 of the tile and all 64 columns; K in steps of 64 through two stages of
 // cp.async copies (rows padded by 16 bytes so that ldmatrix reads without bank conflicts); m16n8k16 products, float sums.
@@ -468,6 +552,41 @@ MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, con
         return fail("expert_product: unknown dtype code %d", dtype);
     }
 #undef MB_PRODUCT
+    return 0;
+}
+
+// The products for few entries (see expert_rows_kernel); rows of mid and slot_out in entry order (token * top + choice).
+MB_EXPORT int mb_expert_rows(const void* a, int a_stride, const void* w0, const void* w1, void* mid, float* slot_out, int out_stride,
+                             int dtype, const int* chosen, int entries, int top, int experts, int N, int K, float limit, float slope,
+                             int first, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (N <= 0 || K <= 0 || top <= 0 || experts <= 0) return fail("expert_rows: N %d, K %d, top %d, %d experts", N, K, top, experts);
+    if (entries > 65535) return fail("expert_rows: %d entries exceed the grid limit 65535", entries);
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 200 * 1024) return fail("expert_rows: a row of %d elements exceeds a block's shared memory", K);
+    const dim3 grid((N + 31) / 32, entries);
+    const size_t unit = dtype == MB_F32 ? 32 : 16;
+    const size_t element = dtype == MB_F32 ? 4 : 2;
+    const bool vector = K % 8 == 0 && ((size_t)a_stride * element) % unit == 0 && !((uintptr_t)a % unit) && !((uintptr_t)w0 % unit) &&
+                        !((uintptr_t)w1 % unit);
+#define MB_ROWS(T, FIRST, VECTOR)                                                                                                    \
+    do {                                                                                                                             \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<T, FIRST, VECTOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        MB_LAUNCH("expert_rows", (expert_rows_kernel<T, FIRST, VECTOR>), grid, dim3(256), smem, stream, true, (const T*)a, a_stride,  \
+                  (const T*)w0, (const T*)w1, (T*)mid, slot_out, out_stride, chosen, top, experts, N, K, limit, slope);               \
+    } while (0)
+#define MB_ROWS_OF(T)                                                              \
+    do {                                                                           \
+        if (first && vector) MB_ROWS(T, true, true);                               \
+        else if (first) MB_ROWS(T, true, false);                                   \
+        else if (vector) MB_ROWS(T, false, true);                                  \
+        else MB_ROWS(T, false, false);                                             \
+    } while (0)
+    if (dtype == MB_F32) MB_ROWS_OF(float);
+    else if (dtype == MB_BF16) MB_ROWS_OF(__nv_bfloat16);
+    else return fail("expert_rows: unknown dtype code %d", dtype);
+#undef MB_ROWS_OF
+#undef MB_ROWS
     return 0;
 }
 

@@ -1640,6 +1640,49 @@ def expert_second_product(mid: torch.Tensor, down_w: torch.Tensor, plan: RoutePl
     return slot_out
 
 
+EXPERT_ROWS_ENTRIES = 64  # up to so many (token, choice) entries a step's experts run entry by entry, without sorting
+
+
+def expert_rows_first(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, chosen: torch.Tensor, limit: float,
+                      slope: float) -> torch.Tensor:
+    """The first product for a step of few tokens: mid [tokens * top, n] (row token * top + choice, x's dtype), each row
+    clamped_swish(gate_w[e] . x, up_w[e] . x) for its token's row x and its chosen expert e.  Every entry streams its
+    expert's matrices once; nothing is sorted."""
+    _cuda(x, gate_w, up_w, chosen)
+    _columns(x, "x")
+    _int32(chosen, "chosen")
+    experts = gate_w.shape[0]
+    _expert_weights(gate_w, experts, "expert_rows_first")
+    _expert_weights(up_w, experts, "expert_rows_first")
+    if gate_w.shape != up_w.shape or gate_w.shape[2] != x.shape[1] or not (gate_w.dtype == up_w.dtype == x.dtype) \
+            or chosen.dim() != 2 or chosen.shape[0] != x.shape[0] or not chosen.is_contiguous():
+        raise KernelError(f"expert_rows_first: matrices {tuple(gate_w.shape)} / {tuple(up_w.shape)} and choices {tuple(chosen.shape)} "
+                          f"do not fit rows {tuple(x.shape)}")
+    n, k, top = gate_w.shape[1], gate_w.shape[2], chosen.shape[1]
+    mid = torch.empty((chosen.numel(), n), dtype=x.dtype, device=x.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_expert_rows(_p(x), x.stride(0), _p(gate_w), _p(up_w), _p(mid), None, n, _code(x.dtype), _p(chosen), chosen.numel(),
+                                 top, experts, n, k, ctypes.c_float(limit), ctypes.c_float(slope), 1, _stream()))
+    return mid
+
+
+def expert_rows_second(mid: torch.Tensor, down_w: torch.Tensor, chosen: torch.Tensor) -> torch.Tensor:
+    """slot_out float32 [tokens * top, n]: row i is down_w[e_i] . mid[i] for entry i's chosen expert (float32 sums)."""
+    _cuda(mid, down_w, chosen)
+    _int32(chosen, "chosen")
+    experts = down_w.shape[0]
+    _expert_weights(down_w, experts, "expert_rows_second")
+    if mid.dim() != 2 or not mid.is_contiguous() or mid.shape[0] != chosen.numel() or down_w.shape[2] != mid.shape[1] \
+            or down_w.dtype != mid.dtype or not chosen.is_contiguous():
+        raise KernelError(f"expert_rows_second: matrices {tuple(down_w.shape)} do not fit rows {tuple(mid.shape)}")
+    n, k = down_w.shape[1], down_w.shape[2]
+    slot_out = torch.empty((mid.shape[0], n), dtype=torch.float32, device=mid.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_expert_rows(_p(mid), mid.stride(0), _p(down_w), None, None, _p(slot_out), n, _code(mid.dtype), _p(chosen),
+                                 chosen.numel(), chosen.shape[1], experts, n, k, ctypes.c_float(0.0), ctypes.c_float(0.0), 0, _stream()))
+    return slot_out
+
+
 def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> None:
     """out = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and up column
     slices of one tensor."""

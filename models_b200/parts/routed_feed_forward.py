@@ -7,7 +7,8 @@ and is added multiplied by sigmoid(w.xn), one number per token.
 
 The step's (token, choice) entries are sorted by expert on the device; the experts' two products are then grouped products
 over the sorted rows (a block a tile of one expert's rows), whose grids depend on the number of tokens only -- nothing comes
-back to the host, so a step can be captured.  The shared expert's gate, up and score rows are one dense product.  The result
+back to the host, so a step can be captured.  A step of few entries (decoding) skips the sorting: every entry streams its
+expert's matrices through a kernel of dot products, which is what the memory allows at that size.  The shared expert's gate, up and score rows are one dense product.  The result
 is float32 [tokens, width]: the weighted sum of the chosen experts' float32 results plus the shared expert's.
 """
 
@@ -69,9 +70,14 @@ class RoutedFeedForward(Part):
         s = self.spec
         x = xn if xn.dtype == self.router.dtype else xn.to(self.router.dtype)
         chosen, weights = ops.router_topk(x, self.router, s.top)
-        plan = ops.route_sort(chosen, s.num_experts)
-        mid = ops.expert_first_product(x, self.w_gate, self.w_up, plan, s.expert.limit, s.expert.swish_slope)
-        slot_out = ops.expert_second_product(mid, self.w_down, plan)
+        if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
+            # a decode step: every entry streams its expert's matrices; no sorting, no tiles of mostly empty rows
+            mid = ops.expert_rows_first(x, self.w_gate, self.w_up, chosen, s.expert.limit, s.expert.swish_slope)
+            slot_out = ops.expert_rows_second(mid, self.w_down, chosen)
+        else:
+            plan = ops.route_sort(chosen, s.num_experts)
+            mid = ops.expert_first_product(x, self.w_gate, self.w_up, plan, s.expert.limit, s.expert.swish_slope)
+            slot_out = ops.expert_second_product(mid, self.w_down, plan)
         if self.shared_in is None:
             return ops.expert_combine(slot_out, weights)
         dtype = self.runtime.compute_dtype

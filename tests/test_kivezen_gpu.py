@@ -167,7 +167,7 @@ KERNEL_TOLERANCE = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,rot,page", [
-    (1, 1, 8, 8, None, 32), (6, 2, 20, 12, (10, 3000.0, (2.0, 32, 8.0, 2.0)), 64), (3, 3, 40, 72, (40, 50.0), 128),
+    (1, 1, 8, 8, None, 32), (3, 1, 9, 6, None, 32), (6, 2, 20, 12, (10, 3000.0, (2.0, 32, 8.0, 2.0)), 64), (3, 3, 40, 72, (40, 50.0), 128),
     (4, 1, 64, 128, (32, 1e5, (4.0, 128, 16.0, 1.0)), 64), (2, 2, 18, 14, (0, 100.0), 64), (8, 4, 32, 160, (16, 1e4), 64)])
 def test_capped_attention_sizes_rotation_cap_sink_in_every_form(cuda_device, heads, kv_heads, dim, vdim, rot, page, dtype):
     """Random heads: a whole prompt (the tensor-core form where it applies, and the form with a warp per row), a prompt's last
@@ -303,6 +303,13 @@ def test_routed_experts(cuda_device, experts, top, width, ff, tokens, dtype):
         mlp = {"router": {"experts": experts, "top": top}, "expert": {"limit": limit}}
         want = pk.routed_feed_forward(x, names, "", mlp)
         assert scaled_error(got, want) < KERNEL_TOLERANCE[dtype], tensor_cores
+    # the form for few entries (entry by entry, nothing sorted); here with any number of them, also on rows of a wider tensor
+    wide = torch.zeros((tokens, width + 8), dtype=dtype, device=cuda_device)
+    wide[:, :width] = xd
+    for rows in (xd, wide[:, :width]):
+        by_entry = ops.expert_rows_second(ops.expert_rows_first(rows, stack("gate"), stack("up"), chosen, limit, pk.SWISH_SLOPE),
+                                          stack("down"), chosen)
+        assert scaled_error(ops.expert_combine(by_entry, weights), want) < KERNEL_TOLERANCE[dtype]
     shared = torch.randn(tokens, width, generator=g, dtype=F)
     score = _rounded(torch.randn(tokens, 1, generator=g, dtype=F), dtype)
     got = ops.expert_combine(slot_out, weights, shared.float().contiguous().to(cuda_device), dev(score))
