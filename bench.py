@@ -725,7 +725,8 @@ def kivezen_kernels(z, peak, prompt=2048, batch=8, context=1536):
         # width is what a token uses (top experts side by side), through the products the package gives a dense layer
         x = torch.randn((rows, W), device=dev).to(bf)
         router = (torch.randn((E, W), device=dev) * 0.02).to(bf)
-        w_gate, w_up = ((torch.randn((E, F, W), device=dev) * 0.02).to(bf) for _ in range(2))
+        w_gate_up = (torch.randn((2, E, F, W), device=dev) * 0.02).to(bf)
+        w_gate, w_up = w_gate_up[0], w_gate_up[1]
         w_down = (torch.randn((E, W, F), device=dev) * 0.02).to(bf)
 
         def routed():  # (as the model's feed-forward runs them)
@@ -733,6 +734,10 @@ def kivezen_kernels(z, peak, prompt=2048, batch=8, context=1536):
             if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
                 mid = ops.expert_rows_first(x, w_gate, w_up, chosen, 7.0, 1.702)
                 return ops.expert_combine(ops.expert_rows_second(mid, w_down, chosen), weights)
+            if chosen.numel() >= ops.GROUPED_ROWS_PER_EXPERT * E:
+                plan = ops.route_pad(chosen, E)
+                mid = ops.grouped_first_product(ops.gather_rows(x, plan), w_gate_up, plan, 7.0, 1.702)
+                return ops.expert_combine(ops.grouped_second_product(mid, w_down, plan), weights, position=plan.position)
             plan = ops.route_sort(chosen, E)
             mid = ops.expert_first_product(x, w_gate, w_up, plan, 7.0, 1.702)
             return ops.expert_combine(ops.expert_second_product(mid, w_down, plan), weights)

@@ -131,7 +131,15 @@ struct GemmArgs {
     const float* sin_table;
     bf16* k_pool;             // [pages][kv_heads][page_size][head_dim]
     bf16* v_pool;
+    // A grouped product: the rows of every tile of 128 rows of A belong to one group (an expert of a mixture), and W holds
+    // the groups' matrices one below the other.  tile_group [tiles of 128 rows]: the tile's group, or < 0 for a tile nobody
+    // reads (it is left out; its rows of the output are not written).  The table is written by a kernel before.
+    const int* tile_group;    // null: a plain product
+    int group_rows;           // rows of W per group (EPI_SWIGLU: gate rows; the up rows of the same group lie up_row_offset further)
+    float limit, slope;       // activation kClampedSwish: min(gate, limit) * sigmoid(slope * that) * (clamp(up, -limit, limit) + 1)
 };
+
+constexpr int kClampedSwish = 100;  // (beside the MB_ACT_* codes; only the grouped entry point sets it)
 
 // kPair 1: a block works on a tile alone.  kPair 2: the two blocks of a cluster share a tile of 256 rows by BN columns
 // (tcgen05 cta_group::2): each loads its 128 rows of A and its half of the BN rows of W, the leader issues the products
@@ -181,6 +189,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int k_blocks_all = (args.k + kBlockK - 1) / kBlockK;
     const int k_blocks_per_split = (k_blocks_all + k_splits - 1) / k_splits;  // the launcher leaves no part empty
     const int first_tile = blockIdx.x / kPair, tile_step = gridDim.x / kPair;  // a pair walks the tiles together
+    // A grouped product leaves out the tiles of rows that belong to no group: every role asks the same table (after it has
+    // waited for the kernels before), so all of them leave out the same tiles.  (Grouped products run on single blocks.)
+    auto nobody_reads = [&](int tile) {
+        if (args.tile_group == nullptr) return false;
+        int m_tile, n_tile;
+        tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+        return args.tile_group[m_tile] < 0;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -239,7 +255,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // The weights depend on nothing: the first tile's first stages of them are asked for before this kernel waits
             // for the one before it; the activations, which that kernel wrote, after.
             int early = 0;
-            if (first_tile < tiles) {
+            if (args.tile_group != nullptr) {
+                grid_dependency_wait();  // which matrix a tile needs is in a table the kernel before wrote
+            } else if (first_tile < tiles) {
                 int m_tile, n_tile;
                 tile_coordinates(first_tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
                 const int kb_begin = (first_tile % k_splits) * k_blocks_per_split, kb_end = min(kb_begin + k_blocks_per_split, k_blocks_all);
@@ -260,12 +278,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
             for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+                if (nobody_reads(tile)) continue;
                 int m_tile, n_tile;
                 tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
                 const int kb_begin = (tile % k_splits) * k_blocks_per_split, kb_end = min(kb_begin + k_blocks_per_split, k_blocks_all);
                 const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
-                const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
-                const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
+                const int group_row = args.tile_group != nullptr ? max(args.tile_group[m_tile], 0) * args.group_rows : 0;
+                const int w_row0 = group_row + (EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN);
+                const int w_row1 = group_row + (EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128);
                 for (int kb = kb_begin + (tile == first_tile ? early : 0); kb < kb_end; ++kb) {
                     if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
                     announce(stage);
@@ -284,7 +304,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 1;  // both accumulators start free
             bool ok = true;
+            if (args.tile_group != nullptr) grid_dependency_wait();
             for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+                if (nobody_reads(tile)) continue;
                 if (!(ok = mbar_wait(acc_empty_bar + 8 * acc, acc_phase, 2))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * kAccumulatorColumns;
@@ -328,6 +350,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+            if (nobody_reads(tile)) continue;
             int m_tile, n_tile;
             tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
             const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
@@ -445,7 +468,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 tmem_load_32_issue(taddr + 128 + c + 32 * part, u);
                                 tmem_load_wait();
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) v[i] = gate_activation(args.activation, v[i]) * u[i];
+                                for (int i = 0; i < 32; ++i) {
+                                    if (args.activation == kClampedSwish) {
+                                        const float g = fminf(v[i], args.limit), up = fminf(fmaxf(u[i], -args.limit), args.limit);
+                                        v[i] = g / (1.0f + expf(-args.slope * g)) * (up + 1.0f);
+                                    } else {
+                                        v[i] = gate_activation(args.activation, v[i]) * u[i];
+                                    }
+                                }
                             } else {
                                 tmem_load_32_issue(taddr + c + 32 * part, v);
                                 tmem_load_wait();
@@ -811,6 +841,30 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
             return launch_tile<EPI_SWIGLU, 256, 1>(map_a, map_w, args, multiprocessors, stream);
     }
     return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+}
+
+// A grouped product (see GemmArgs::tile_group): a bfloat16 [m, k], m a multiple of 128 with every 128 rows of one group;
+// w bfloat16 [w_rows, k], the groups' matrices one below the other.
+// gated != 0: w holds every group's `n` gate rows (group g at row g * n) and, `up_row_offset` rows further, its `n` up
+//             rows; out bfloat16 [m, n] = clamped_swish(gate, up) with `limit` and `slope`.
+// gated == 0: group g's `n` rows at row g * n; out float32 [m, n].
+MB_EXPORT int mb_gemm_tcgen05_grouped(const void* a, int lda, const void* w, int ldw, int w_rows, void* out, int ld_out, int m, int n,
+                                      int k, int gated, int up_row_offset, const int* tile_group, float limit, float slope,
+                                      int multiprocessors, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (tile_group == nullptr) return fail("gemm_tcgen05_grouped: the table of the tiles' groups is missing");
+    if (m % kBlockM) return fail("gemm_tcgen05_grouped: %d rows are no multiple of %d", m, kBlockM);
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05_grouped: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return fail("gemm_tcgen05_grouped: operands must start on 16-byte boundaries");
+    if (((uintptr_t)out & 15) || ld_out % (gated ? 8 : 4)) return fail("gemm_tcgen05_grouped: output rows must start on 16-byte boundaries");
+    CUtensorMap map_a, map_w;
+    if (int status = make_map(&map_a, a, m, k, lda)) return status;
+    if (int status = make_map(&map_w, w, w_rows, k, ldw)) return status;
+    GemmArgs args{};
+    args.m = m; args.n = n; args.k = k; args.up_row_offset = up_row_offset; args.activation = kClampedSwish; args.k_splits = 1;
+    args.out = out; args.ld_out = ld_out; args.tile_group = tile_group; args.group_rows = n; args.limit = limit; args.slope = slope;
+    if (gated) return launch_tile<EPI_SWIGLU, 256, 1>(map_a, map_w, args, multiprocessors, stream);
+    return launch_tile<EPI_F32, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
 
 // The q/k/v product of an attention layer for a whole prompt, with the rotation of queries and keys and the paged

@@ -30,29 +30,79 @@ __device__ __forceinline__ float clamped_swish(float g, float u, float limit, fl
     return g * sigmoid(slope * g) * (u + 1.0f);
 }
 
-// grid (tokens); block 128.  shared: width floats (the token's row), experts floats (its logits).
-template <typename T>
-__global__ void __launch_bounds__(128)
+// grid (ceil(tokens / kTokens)); block 256.  shared per token of the block: width floats (its row), experts floats (its logits).
+// kVector: width a multiple of 8 and rows on 16 (bfloat16) or 32 (float) bytes: a lane reads 8 elements of a router row with
+// one or two wide loads, and a warp works on 4 experts at once so that as many loads are in flight.  kTokens > 1 (prompts):
+// what a lane has loaded of the router serves so many tokens.  A token's sums are taken in the same order whatever kTokens is.
+template <typename T, bool kVector, int kTokens>
+__global__ void __launch_bounds__(256)
 router_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int* __restrict__ chosen,
-                   float* __restrict__ weights, int width, int experts, int top) {
+                   float* __restrict__ weights, int tokens, int width, int experts, int top) {
     grid_launch_dependents();
     grid_dependency_wait();
-    extern __shared__ float router_shared[];
-    float* row = router_shared;
-    float* logits = router_shared + width;
-    __shared__ float picked[kMaxTop];
-    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = Num<T>::load(x + (size_t)token * x_stride + c);
-    __syncthreads();
-    for (int e = warp; e < experts; e += warps) {
-        const T* w = router + (size_t)e * width;
-        float sum = 0.0f;
-        for (int c = lane; c < width; c += 32) sum = fmaf(row[c], Num<T>::load(w + c), sum);
-        sum = warp_sum(sum);
-        if (lane == 0) logits[e] = sum;
+    extern __shared__ __align__(16) float router_shared[];
+    float* rows = router_shared;                       // [kTokens][width]
+    float* all_logits = router_shared + kTokens * width;  // [kTokens][experts]
+    __shared__ float all_picked[kTokens][kMaxTop];
+    const int token0 = blockIdx.x * kTokens, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int here = min(kTokens, tokens - token0);
+    if (kVector) {
+        for (int c = threadIdx.x; c < kTokens * (width / 8); c += blockDim.x) {
+            const int t = c / (width / 8), piece = c % (width / 8);
+            float v[8];
+            load8(x + (size_t)min(token0 + t, tokens - 1) * x_stride + piece * 8, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rows[t * width + piece * 8 + i] = v[i];
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) rows[c] = Num<T>::load(x + (size_t)token0 * x_stride + c);
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (kVector) {
+        constexpr int kAtOnce = 4;
+        for (int e0 = warp * kAtOnce; e0 < experts; e0 += warps * kAtOnce) {
+            float sum[kTokens][kAtOnce];
+#pragma unroll
+            for (int t = 0; t < kTokens; ++t)
+#pragma unroll
+                for (int j = 0; j < kAtOnce; ++j) sum[t][j] = 0.0f;
+            for (int c = lane; c < width / 8; c += 32) {
+                float w[kAtOnce][8];
+#pragma unroll
+                for (int j = 0; j < kAtOnce; ++j) load8(router + (size_t)min(e0 + j, experts - 1) * width + c * 8, w[j]);
+#pragma unroll
+                for (int t = 0; t < kTokens; ++t) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(rows + t * width + c * 8);
+                    const float4 x1 = *reinterpret_cast<const float4*>(rows + t * width + c * 8 + 4);
+                    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int j = 0; j < kAtOnce; ++j)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) sum[t][j] = fmaf(xs[i], w[j][i], sum[t][j]);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kTokens; ++t)
+#pragma unroll
+                for (int j = 0; j < kAtOnce; ++j) {
+                    const float total = warp_sum(sum[t][j]);
+                    if (lane == 0 && e0 + j < experts) all_logits[t * experts + e0 + j] = total;
+                }
+        }
+    } else {
+        for (int e = warp; e < experts; e += warps) {
+            const T* w = router + (size_t)e * width;
+            float sum = 0.0f;
+            for (int c = lane; c < width; c += 32) sum = fmaf(rows[c], Num<T>::load(w + c), sum);
+            sum = warp_sum(sum);
+            if (lane == 0) all_logits[e] = sum;
+        }
+    }
+    __syncthreads();
+    if (warp >= here) return;  // warp t picks for the block's token t
+    const int token = token0 + warp;
+    float* logits = all_logits + warp * experts;
+    float* picked = all_picked[warp];
     for (int s = 0; s < top; ++s) {
         // the largest logit that is not taken yet; ties go to the lower index (a taken expert's logit is -inf)
         float best = -CUDART_INF_F;
@@ -132,6 +182,158 @@ route_sort_kernel(const int* __restrict__ chosen, int entries, int experts, int*
             at += __popc(mask);
         }
     }
+}
+
+// The same result for up to kFastExperts experts in three sweeps: every warp owns a stretch of the entries, counts its
+// stretch per expert (lanes with the same expert find one another with a match), the counts become each warp's first place
+// per expert, and the warp then puts its entries there in their order.  shared: counts [32][experts], totals [experts],
+// starts [experts + 1].
+constexpr int kFastExperts = 256;
+
+__global__ void __launch_bounds__(1024)
+route_sort_fast_kernel(const int* __restrict__ chosen, int entries, int experts, int* __restrict__ offsets, int* __restrict__ sorted,
+                       int* __restrict__ tile_expert, int* __restrict__ tile_row, int max_tiles) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ int sort_shared[];
+    int* counts = sort_shared;                 // [32][experts]
+    int* totals = sort_shared + 32 * experts;  // [experts]
+    int* starts = totals + experts;            // [experts + 1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 32 * experts; i += blockDim.x) counts[i] = 0;
+    __syncthreads();
+    const int stretch = ((entries + 32 * 32 - 1) / (32 * 32)) * 32;  // entries per warp, a multiple of 32
+    const int first = warp * stretch, last = min(first + stretch, entries);
+    int* mine = counts + warp * experts;
+    for (int base = first; base < last; base += 32) {
+        const int i = base + lane;
+        int e = i < last ? chosen[i] : -1;
+        if (e < 0 || e >= experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int count = counts[w * experts + e];
+            counts[w * experts + e] = run;
+            run += count;
+        }
+        totals[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < experts; ++e) {
+            starts[e] = at;
+            offsets[e] = at;
+            for (int r = 0; r < totals[e] && tile < max_tiles; r += kTileRows) {
+                tile_expert[tile] = e;
+                tile_row[tile] = at + r;
+                ++tile;
+            }
+            at += totals[e];
+        }
+        starts[experts] = at;
+        offsets[experts] = at;
+        for (; tile < max_tiles; ++tile) tile_expert[tile] = -1, tile_row[tile] = 0;
+    }
+    __syncthreads();
+    for (int base = first; base < last; base += 32) {
+        const int i = base + lane;
+        int e = i < last ? chosen[i] : -1;
+        if (e < 0 || e >= experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) sorted[starts[e] + mine[e] + __popc(same & ((1u << lane) - 1u))] = i;
+        __syncwarp();
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+    }
+}
+
+// The entries by expert with every expert's rows starting on a multiple of kGroupTile rows, for products whose tiles of
+// that many rows each belong to one expert.  One block of 1024 threads; up to kFastExperts experts (the sweeps of
+// route_sort_fast_kernel).  sorted [max_tiles * kGroupTile]: the entry at every row, -1 at rows that only fill a tile up;
+// position [entries]: the row of every entry; tile_group [max_tiles]: the expert of every tile, -1 past the last one.
+constexpr int kGroupTile = 128;
+
+__global__ void __launch_bounds__(1024)
+route_pad_kernel(const int* __restrict__ chosen, int entries, int experts, int* __restrict__ sorted, int* __restrict__ position,
+                 int* __restrict__ tile_group, int max_tiles) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ int sort_shared[];
+    int* counts = sort_shared;                 // [32][experts]
+    int* totals = sort_shared + 32 * experts;  // [experts]
+    int* starts = totals + experts;            // [experts + 1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 32 * experts; i += blockDim.x) counts[i] = 0;
+    for (int i = threadIdx.x; i < max_tiles * kGroupTile; i += blockDim.x) sorted[i] = -1;
+    __syncthreads();
+    const int stretch = ((entries + 32 * 32 - 1) / (32 * 32)) * 32;
+    const int first = warp * stretch, last = min(first + stretch, entries);
+    int* mine = counts + warp * experts;
+    for (int base = first; base < last; base += 32) {
+        const int i = base + lane;
+        int e = i < last ? chosen[i] : -1;
+        if (e < 0 || e >= experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int count = counts[w * experts + e];
+            counts[w * experts + e] = run;
+            run += count;
+        }
+        totals[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < experts; ++e) {
+            starts[e] = tile * kGroupTile;
+            for (int r = 0; r < totals[e] && tile < max_tiles; r += kGroupTile) tile_group[tile++] = e;
+        }
+        for (; tile < max_tiles; ++tile) tile_group[tile] = -1;
+    }
+    __syncthreads();
+    for (int base = first; base < last; base += 32) {
+        const int i = base + lane;
+        int e = i < last ? chosen[i] : -1;
+        if (e < 0 || e >= experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+            const int at = starts[e] + mine[e] + __popc(same & ((1u << lane) - 1u));
+            sorted[at] = i;
+            position[i] = at;
+        }
+        __syncwarp();
+        if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+        __syncwarp();
+    }
+    for (int i = first + lane; i < last; i += 32)  // (an entry whose expert does not exist reads row 0; its weight is what the router gave)
+        if (chosen[i] < 0 || chosen[i] >= experts) position[i] = 0;
+}
+
+// grid (max_tiles * kGroupTile); block 128.  out [row][K] = x [sorted[row] / top][K], zeros at rows that fill a tile up;
+// rows of tiles past the last one are left as they are.  K a multiple of 8 bfloat16, rows on 16 bytes.
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const int* __restrict__ sorted, const int* __restrict__ tile_group,
+                   __nv_bfloat16* __restrict__ out, int top, int K) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int row = blockIdx.x;
+    if (tile_group[row / kGroupTile] < 0) return;
+    const int entry = sorted[row];
+    const uint4* src = entry >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)(entry / top) * x_stride) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * K);
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src != nullptr ? src[c] : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // The grouped product in plain float arithmetic.  grid (ceil(N / 64), max_tiles); block 256 (16 x 16; a thread 4 x 4).
@@ -449,10 +651,11 @@ __global__ void clamped_swish_kernel(const T* __restrict__ gate, const T* __rest
 }
 
 // out[t][c] = sum_s weights[t][s] * slot_out[t * top + s][c] (+ sigmoid(score[t]) * shared[t][c]); float out.
+// `position` (or null): entry t * top + s has its row of slot_out at position[t * top + s] instead.
 template <typename T>
 __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const float* __restrict__ weights,
                                       const float* __restrict__ shared, const T* __restrict__ score, int score_stride,
-                                      float* __restrict__ out, size_t total, int width, int top) {
+                                      float* __restrict__ out, size_t total, int width, int top, const int* __restrict__ position) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -460,7 +663,10 @@ __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const 
     const size_t t = i / width;
     const int c = (int)(i % width);
     float sum = 0.0f;
-    for (int s = 0; s < top; ++s) sum = fmaf(weights[t * top + s], slot_out[(t * top + s) * width + c], sum);
+    for (int s = 0; s < top; ++s) {
+        const size_t row = position != nullptr ? (size_t)position[t * top + s] : t * top + s;  // where the entry's result lies
+        sum = fmaf(weights[t * top + s], slot_out[row * width + c], sum);
+    }
     if (shared != nullptr) sum = fmaf(sigmoid(Num<T>::load(score + t * score_stride)), shared[i], sum);
     out[i] = sum;
 }
@@ -477,19 +683,28 @@ MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, in
     if (tokens <= 0) return 0;
     if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > kMaxTop)
         return fail("router_topk: width %d, %d experts, top %d (at most %d and the number of experts)", width, experts, top, kMaxTop);
-    const size_t smem = ((size_t)width + experts) * sizeof(float);
-    if (smem > 200 * 1024) return fail("router_topk: a row of %d and %d logits exceed a block's shared memory", width, experts);
+    const size_t one = ((size_t)width + experts) * sizeof(float);
+    if (one > 200 * 1024) return fail("router_topk: a row of %d and %d logits exceed a block's shared memory", width, experts);
+    const size_t unit = dtype == MB_F32 ? 32 : 16, element = dtype == MB_F32 ? 4 : 2;
+    const bool vector = width % 8 == 0 && ((size_t)x_stride * element) % unit == 0 && !((uintptr_t)x % unit) && !((uintptr_t)router % unit);
+    constexpr int kTogether = 4;  // tokens of a prompt that share what a block loads of the router
+    const bool together = vector && tokens >= 64 * kTogether && kTogether * one <= 200 * 1024;
+#define MB_ROUTER(T, VECTOR, TOKENS)                                                                                                  \
+    do {                                                                                                                              \
+        const size_t smem = TOKENS * one;                                                                                             \
+        if (smem > 48 * 1024)                                                                                                         \
+            cudaFuncSetAttribute(router_topk_kernel<T, VECTOR, TOKENS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        MB_LAUNCH("router_topk", (router_topk_kernel<T, VECTOR, TOKENS>), dim3((tokens + TOKENS - 1) / TOKENS), dim3(256), smem, stream, \
+                  true, (const T*)x, x_stride, (const T*)router, chosen, weights, tokens, width, experts, top);                       \
+    } while (0)
     if (dtype == MB_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("router_topk", router_topk_kernel<float>, dim3(tokens), dim3(128), smem, stream, true, (const float*)x, x_stride,
-                  (const float*)router, chosen, weights, width, experts, top);
+        if (together) MB_ROUTER(float, true, kTogether); else if (vector) MB_ROUTER(float, true, 1); else MB_ROUTER(float, false, 1);
     } else if (dtype == MB_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("router_topk", router_topk_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, stream, true, (const __nv_bfloat16*)x,
-                  x_stride, (const __nv_bfloat16*)router, chosen, weights, width, experts, top);
+        if (together) MB_ROUTER(__nv_bfloat16, true, kTogether); else if (vector) MB_ROUTER(__nv_bfloat16, true, 1); else MB_ROUTER(__nv_bfloat16, false, 1);
     } else {
         return fail("router_topk: unknown dtype code %d", dtype);
     }
+#undef MB_ROUTER
     return 0;
 }
 
@@ -500,8 +715,37 @@ MB_EXPORT int mb_route_sort(const int* chosen, int entries, int experts, int* of
     if (entries <= 0) return 0;
     if (experts <= 0 || experts > 4096) return fail("route_sort: %d experts (at most 4096)", experts);
     if (max_tiles < mb_route_max_tiles(entries, experts)) return fail("route_sort: room for %d tiles, %d may be needed", max_tiles, mb_route_max_tiles(entries, experts));
+    if (experts <= kFastExperts) {
+        MB_LAUNCH("route_sort", route_sort_fast_kernel, dim3(1), dim3(1024), (34 * (size_t)experts + 1) * sizeof(int), stream, true, chosen,
+                  entries, experts, offsets, sorted, tile_expert, tile_row, max_tiles);
+        return 0;
+    }
     MB_LAUNCH("route_sort", route_sort_kernel, dim3(1), dim3(1024), (2 * (size_t)experts + 1) * sizeof(int), stream, true, chosen, entries,
               experts, offsets, sorted, tile_expert, tile_row, max_tiles);
+    return 0;
+}
+
+MB_EXPORT int mb_route_group_tile() { return kGroupTile; }
+MB_EXPORT int mb_route_pad_max_experts() { return kFastExperts; }
+MB_EXPORT int mb_route_pad_max_tiles(int entries, int experts) { return (entries + kGroupTile - 1) / kGroupTile + experts; }
+
+// sorted [max_tiles * 128], position [entries], tile_group [max_tiles]: see route_pad_kernel.
+MB_EXPORT int mb_route_pad(const int* chosen, int entries, int experts, int* sorted, int* position, int* tile_group, int max_tiles,
+                           cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (experts <= 0 || experts > kFastExperts) return fail("route_pad: %d experts (at most %d)", experts, kFastExperts);
+    if (max_tiles < mb_route_pad_max_tiles(entries, experts)) return fail("route_pad: room for %d tiles, %d may be needed", max_tiles, mb_route_pad_max_tiles(entries, experts));
+    MB_LAUNCH("route_pad", route_pad_kernel, dim3(1), dim3(1024), (34 * (size_t)experts + 1) * sizeof(int), stream, true, chosen, entries,
+              experts, sorted, position, tile_group, max_tiles);
+    return 0;
+}
+
+MB_EXPORT int mb_gather_rows(const void* x, int x_stride, const int* sorted, const int* tile_group, void* out, int rows, int top, int K,
+                             cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (K <= 0 || K % 8 || x_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return fail("gather_rows: rows of %d elements (stride %d) must be multiples of 8 on 16-byte boundaries", K, x_stride);
+    MB_LAUNCH("gather_rows", gather_rows_kernel, dim3(rows), dim3(128), 0, stream, true, (const __nv_bfloat16*)x, x_stride, sorted,
+              tile_group, (__nv_bfloat16*)out, top, K);
     return 0;
 }
 
@@ -608,17 +852,17 @@ MB_EXPORT int mb_clamped_swish(const void* gate, const void* up, int in_stride, 
 
 // shared may be null (no shared expert); score is one number per token of the storage type `dtype` (stride in elements).
 MB_EXPORT int mb_expert_combine(const float* slot_out, const float* weights, const float* shared, const void* score, int score_stride,
-                                int dtype, float* out, int tokens, int width, int top, cudaStream_t stream) {
+                                int dtype, float* out, int tokens, int width, int top, const int* position, cudaStream_t stream) {
     if (tokens <= 0 || width <= 0) return 0;
     if (shared != nullptr && score == nullptr) return fail("expert_combine: a shared expert needs its gate scores");
     const size_t total = (size_t)tokens * width;
     const dim3 grid((unsigned)((total + 255) / 256));
     if (dtype == MB_F32)
         MB_LAUNCH("expert_combine", expert_combine_kernel<float>, grid, dim3(256), 0, stream, true, slot_out, weights, shared, (const float*)score,
-                  score_stride, out, total, width, top);
+                  score_stride, out, total, width, top, position);
     else if (dtype == MB_BF16)
         MB_LAUNCH("expert_combine", expert_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, slot_out, weights, shared,
-                  (const __nv_bfloat16*)score, score_stride, out, total, width, top);
+                  (const __nv_bfloat16*)score, score_stride, out, total, width, top, position);
     else
         return fail("expert_combine: unknown dtype code %d", dtype);
     return 0;

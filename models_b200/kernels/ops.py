@@ -1640,6 +1640,95 @@ def expert_second_product(mid: torch.Tensor, down_w: torch.Tensor, plan: RoutePl
     return slot_out
 
 
+class PaddedRoutePlan:
+    """The entries of a step grouped by expert with every expert's rows starting on a multiple of `tile` rows, for grouped
+    products on the tensor cores whose tiles of rows each belong to one expert.  `sorted` [rows]: the entry at every row (-1
+    at rows that fill a tile up), `position` [entries]: the row of every entry, `tile_group` [tiles]: the expert of every
+    tile (-1 past the last one)."""
+
+    def __init__(self, chosen: torch.Tensor, experts: int):
+        lib = routed_experts_library()
+        self.entries = chosen.numel()
+        self.top = chosen.shape[1]
+        self.experts = experts
+        self.tile = lib.mb_route_group_tile()
+        self.max_tiles = lib.mb_route_pad_max_tiles(self.entries, experts)
+        self.rows = self.max_tiles * self.tile
+        ints = torch.empty((self.rows + self.entries + self.max_tiles,), dtype=torch.int32, device=chosen.device)
+        self.sorted = ints[:self.rows]
+        self.position = ints[self.rows:self.rows + self.entries]
+        self.tile_group = ints[self.rows + self.entries:]
+        _run(lib, lib.mb_route_pad(_p(chosen), self.entries, experts, _p(self.sorted), _p(self.position), _p(self.tile_group),
+                                   self.max_tiles, _stream()))
+
+
+def route_pad_takes(experts: int) -> bool:
+    return experts <= routed_experts_library().mb_route_pad_max_experts()
+
+
+def route_pad(chosen: torch.Tensor, experts: int) -> PaddedRoutePlan:
+    _cuda(chosen)
+    _int32(chosen, "chosen")
+    if chosen.dim() != 2 or not chosen.is_contiguous():
+        raise KernelError("route_pad: chosen must be contiguous [tokens, top]")
+    return PaddedRoutePlan(chosen, experts)
+
+
+def gather_rows(x: torch.Tensor, plan: PaddedRoutePlan) -> torch.Tensor:
+    """bfloat16 [plan.rows, k]: row r is x[plan.sorted[r] // top], zeros at rows that fill a tile up; the rows of tiles past
+    the last one are not written."""
+    _cuda(x)
+    _columns(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise KernelError("gather_rows: bfloat16 rows are needed")
+    out = torch.empty((plan.rows, x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    lib = routed_experts_library()
+    _run(lib, lib.mb_gather_rows(_p(x), x.stride(0), _p(plan.sorted), _p(plan.tile_group), _p(out), plan.rows, plan.top, x.shape[1],
+                                 _stream()))
+    return out
+
+
+def grouped_product_takes(gate_up: torch.Tensor, down: torch.Tensor) -> bool:
+    """Whether the grouped tcgen05 products take these expert matrices: gate_up [2, experts, ff, width] (gate rows of all
+    experts, then up rows), down [experts, width, ff], bfloat16, rows on 16-byte boundaries."""
+    if gate_up.dtype != torch.bfloat16 or down.dtype != torch.bfloat16 or gate_up.dim() != 4 or down.dim() != 3:
+        return False
+    _, experts, ff, width = gate_up.shape
+    return (gate_up.is_contiguous() and down.is_contiguous() and width % 8 == 0 and ff % 8 == 0 and gate_up.data_ptr() % 16 == 0
+            and down.data_ptr() % 16 == 0 and 2 * experts * ff < 2 ** 31 and route_pad_takes(experts))
+
+
+def grouped_first_product(a: torch.Tensor, gate_up: torch.Tensor, plan: PaddedRoutePlan, limit: float, slope: float) -> torch.Tensor:
+    """mid bfloat16 [plan.rows, ff]: for the rows of a tile of expert e, g = min(gate[e] . a, limit),
+    u = clamp(up[e] . a, -limit, limit), mid = g * sigmoid(slope * g) * (u + 1), on the tcgen05 tensor cores."""
+    _cuda(a, gate_up)
+    _, experts, ff, width = gate_up.shape
+    if a.dtype != torch.bfloat16 or not a.is_contiguous() or tuple(a.shape) != (plan.rows, width) or experts != plan.experts:
+        raise KernelError(f"grouped_first_product: rows {tuple(a.shape)} do not fit matrices {tuple(gate_up.shape)}")
+    mid = torch.empty((plan.rows, ff), dtype=torch.bfloat16, device=a.device)
+    lib = gemm_tc()
+    _run(lib, lib.mb_gemm_tcgen05_grouped(_p(a), a.stride(0), _p(gate_up), width, 2 * experts * ff, _p(mid), ff, plan.rows, ff, width,
+                                          1, experts * ff, _p(plan.tile_group), ctypes.c_float(limit), ctypes.c_float(slope),
+                                          _sm_count(a.device), _stream()))
+    return mid
+
+
+def grouped_second_product(mid: torch.Tensor, down: torch.Tensor, plan: PaddedRoutePlan) -> torch.Tensor:
+    """float32 [plan.rows, width]: row r of a tile of expert e is down[e] . mid[r] (float32 sums)."""
+    _cuda(mid, down)
+    experts, width, ff = down.shape
+    if mid.dtype != torch.bfloat16 or not mid.is_contiguous() or tuple(mid.shape) != (plan.rows, ff) or experts != plan.experts:
+        raise KernelError(f"grouped_second_product: rows {tuple(mid.shape)} do not fit matrices {tuple(down.shape)}")
+    out = torch.empty((plan.rows, width), dtype=torch.float32, device=mid.device)
+    lib = gemm_tc()
+    _run(lib, lib.mb_gemm_tcgen05_grouped(_p(mid), ff, _p(down), ff, experts * width, _p(out), width, plan.rows, width, ff, 0, 0,
+                                          _p(plan.tile_group), ctypes.c_float(0.0), ctypes.c_float(0.0), _sm_count(mid.device),
+                                          _stream()))
+    return out
+
+
+GROUPED_ROWS_PER_EXPERT = 32  # from so many entries per expert on average a step pads the experts' rows to tiles of 128
+
 EXPERT_ROWS_ENTRIES = 64  # up to so many (token, choice) entries a step's experts run entry by entry, without sorting
 
 
@@ -1697,13 +1786,16 @@ def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit
 
 
 def expert_combine(slot_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
-                   score: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   score: Optional[torch.Tensor] = None, position: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = sum_s weights[t, s] * slot_out[t * top + s] (+ sigmoid(score[t]) * shared[t]) as float32 [tokens, width];
-    shared float32 [tokens, width], score one number per token ([tokens, 1], may be a column slice)."""
-    _cuda(slot_out, weights, shared, score)
+    shared float32 [tokens, width], score one number per token ([tokens, 1], may be a column slice).  With `position`
+    (int32 [tokens * top]) entry t * top + s has its row of slot_out at position[t * top + s]."""
+    _cuda(slot_out, weights, shared, score, position)
     tokens, top = weights.shape
     width = slot_out.shape[1]
-    if slot_out.dtype != torch.float32 or not slot_out.is_contiguous() or slot_out.shape[0] != tokens * top \
+    if position is not None and (position.dtype != torch.int32 or position.numel() != tokens * top or not position.is_contiguous()):
+        raise KernelError("expert_combine: position must be contiguous int32 [tokens * top]")
+    if slot_out.dtype != torch.float32 or not slot_out.is_contiguous() or (position is None and slot_out.shape[0] != tokens * top) \
             or weights.dtype != torch.float32 or not weights.is_contiguous():
         raise KernelError("expert_combine: slot_out float32 [tokens * top, width] and weights float32 [tokens, top] are needed")
     if (shared is None) != (score is None):
@@ -1715,5 +1807,6 @@ def expert_combine(slot_out: torch.Tensor, weights: torch.Tensor, shared: Option
     out = torch.empty((tokens, width), dtype=torch.float32, device=slot_out.device)
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_combine(_p(slot_out), _p(weights), _p(shared), _p(score), score.stride(0) if score is not None else 0,
-                                    _code(score.dtype) if score is not None else _F32, _p(out), tokens, width, top, _stream()))
+                                    _code(score.dtype) if score is not None else _F32, _p(out), tokens, width, top, _p(position),
+                                    _stream()))
     return out

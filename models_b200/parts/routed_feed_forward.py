@@ -7,7 +7,8 @@ and is added multiplied by sigmoid(w.xn), one number per token.
 
 The step's (token, choice) entries are sorted by expert on the device; the experts' two products are then grouped products
 over the sorted rows (a block a tile of one expert's rows), whose grids depend on the number of tokens only -- nothing comes
-back to the host, so a step can be captured.  A step of few entries (decoding) skips the sorting: every entry streams its
+back to the host, so a step can be captured.  A prompt with enough rows per expert pads every expert's rows to whole tiles
+of 128 and runs both products as grouped tcgen05 products (bfloat16 weights).  A step of few entries (decoding) skips the sorting: every entry streams its
 expert's matrices through a kernel of dot products, which is what the memory allows at that size.  The shared expert's gate, up and score rows are one dense product.  The result
 is float32 [tokens, width]: the weighted sum of the chosen experts' float32 results plus the shared expert's.
 """
@@ -56,7 +57,11 @@ class RoutedFeedForward(Part):
         if len({m.dtype for m in stacked.values()} | {self.router.dtype}) > 1:
             stacked = {r: m.float() for r, m in stacked.items()}
             self.router = self.router.float()
-        self.w_gate, self.w_up, self.w_down = stacked["gate"], stacked["up"], stacked["down"]
+        # gate and up matrices in one buffer (all experts' gate rows, then all up rows): the grouped tensor-core product
+        # reads both through one map
+        self.w_gate_up = torch.stack([stacked["gate"], stacked["up"]], dim=0).contiguous()
+        self.w_gate, self.w_up, self.w_down = self.w_gate_up[0], self.w_gate_up[1], stacked["down"]
+        self.grouped = self.w_gate_up.is_cuda and ops.grouped_product_takes(self.w_gate_up, self.w_down)
         self.shared_in = None
         if s.shared is not None:
             first = [rt.matrix(tensors[n[r]]) for r in ("shared_gate", "shared_up", "shared_gate_score")]
@@ -70,23 +75,29 @@ class RoutedFeedForward(Part):
         s = self.spec
         x = xn if xn.dtype == self.router.dtype else xn.to(self.router.dtype)
         chosen, weights = ops.router_topk(x, self.router, s.top)
+        position = None
         if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
             # a decode step: every entry streams its expert's matrices; no sorting, no tiles of mostly empty rows
             mid = ops.expert_rows_first(x, self.w_gate, self.w_up, chosen, s.expert.limit, s.expert.swish_slope)
             slot_out = ops.expert_rows_second(mid, self.w_down, chosen)
+        elif self.grouped and chosen.numel() >= ops.GROUPED_ROWS_PER_EXPERT * s.num_experts:
+            # a prompt: every expert's rows fill tiles of their own, and both products run on the tcgen05 tensor cores
+            plan = ops.route_pad(chosen, s.num_experts)
+            mid = ops.grouped_first_product(ops.gather_rows(x, plan), self.w_gate_up, plan, s.expert.limit, s.expert.swish_slope)
+            slot_out, position = ops.grouped_second_product(mid, self.w_down, plan), plan.position
         else:
             plan = ops.route_sort(chosen, s.num_experts)
             mid = ops.expert_first_product(x, self.w_gate, self.w_up, plan, s.expert.limit, s.expert.swish_slope)
             slot_out = ops.expert_second_product(mid, self.w_down, plan)
         if self.shared_in is None:
-            return ops.expert_combine(slot_out, weights)
+            return ops.expert_combine(slot_out, weights, position=position)
         dtype = self.runtime.compute_dtype
         proj = linear(xn, self.shared_in, dtype)
         f, at = s.shared.intermediate_size, self.shared_starts
         shared_mid = torch.empty((xn.shape[0], f), dtype=dtype, device=xn.device)
         ops.clamped_swish(proj[:, at[0]:at[0] + f], proj[:, at[1]:at[1] + f], shared_mid, s.shared.limit, s.shared.swish_slope)
         shared = linear(shared_mid, self.shared_down, torch.float32)
-        return ops.expert_combine(slot_out, weights, shared, proj[:, at[2]:at[2] + 1])
+        return ops.expert_combine(slot_out, weights, shared, proj[:, at[2]:at[2] + 1], position)
 
     def forward(self, xn: torch.Tensor, batch=None, run=None) -> torch.Tensor:
         out = self.forward_wide(xn, batch, run)

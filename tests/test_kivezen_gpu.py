@@ -267,9 +267,53 @@ def test_reading_and_writing_the_streams(cuda_device, streams, width, tokens, dt
     assert all(torch.equal(copies[:, s], dev(y)) for s in range(streams))
 
 
+@pytest.mark.parametrize("experts,top,width,ff,tokens", [(4, 2, 64, 40, 70), (7, 3, 200, 136, 333), (16, 1, 128, 264, 500), (3, 3, 72, 8, 129),
+                                                         (33, 4, 96, 48, 64)])
+def test_routed_experts_on_padded_tiles(cuda_device, experts, top, width, ff, tokens):
+    """The prompt form: every expert's rows padded to tiles of 128 (experts with no row, with a few and with more than a tile),
+    both products grouped on the tensor cores (widths and hidden sizes that are no multiples of the tile among them), and the
+    combination through each entry's row."""
+    from models_b200.kernels import ops
+
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(experts * 7 + top)
+    x = _rounded(torch.randn(tokens, width, generator=g, dtype=F), dtype)
+    router = _rounded(torch.randn(experts, width, generator=g, dtype=F) * 0.3, dtype)
+    if experts > 3:
+        router[2] = 0.0
+        router[2, 0] = -50.0  # an expert that only tokens with a very negative first element pick
+        router[0] = router[0] * 4  # one expert with many rows
+        router = _rounded(router, dtype)
+    names = {"router": router}
+    for e in range(experts):
+        names[f"e{e}.gate"], names[f"e{e}.up"] = (_rounded(torch.randn(ff, width, generator=g, dtype=F) * 0.4, dtype) for _ in range(2))
+        names[f"e{e}.down"] = _rounded(torch.randn(width, ff, generator=g, dtype=F) * 0.2, dtype)
+    dev = lambda t: t.to(dtype).contiguous().to(cuda_device)  # noqa: E731
+    xd = dev(x)
+    chosen, weights = ops.router_topk(xd, dev(router), top)
+    want_chosen, _ = pk.route(x, router, top)
+    assert torch.equal(chosen.cpu().long(), want_chosen)
+    stack = lambda role: torch.stack([names[f"e{e}.{role}"] for e in range(experts)])  # noqa: E731
+    gate_up, down = dev(torch.stack([stack("gate"), stack("up")])), dev(stack("down"))
+    assert ops.grouped_product_takes(gate_up, down)
+    plan = ops.route_pad(chosen, experts)
+    position, order, groups = plan.position.cpu().long(), plan.sorted.cpu().long(), plan.tile_group.cpu().long()
+    assert torch.equal(order[position], torch.arange(tokens * top))  # every entry lies at its row
+    assert int((order >= 0).sum()) == tokens * top
+    assert torch.equal(groups[position // plan.tile], want_chosen.reshape(-1))  # in a tile of its expert
+    used = groups[groups >= 0]
+    assert torch.equal(used, used.sort().values) and bool((groups[len(used):] < 0).all())
+    limit = 0.8
+    mid = ops.grouped_first_product(ops.gather_rows(xd, plan), gate_up, plan, limit, pk.SWISH_SLOPE)
+    got = ops.expert_combine(ops.grouped_second_product(mid, down, plan), weights, position=plan.position)
+    want = pk.routed_feed_forward(x, names, "", {"router": {"experts": experts, "top": top}, "expert": {"limit": limit}})
+    assert scaled_error(got, want) < KERNEL_TOLERANCE[dtype]
+    assert ops.gemm_tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,width,ff,tokens", [(6, 2, 64, 40, 1), (12, 4, 256, 80, 300), (3, 3, 50, 33, 77), (5, 1, 72, 36, 130),
-                                                         (40, 8, 128, 64, 9)])
+                                                         (40, 8, 128, 64, 9), (300, 2, 64, 16, 70)])
 def test_routed_experts(cuda_device, experts, top, width, ff, tokens, dtype):
     """Router choices (ties to the lower index), the softmax over the chosen logits, the grouped products with few and many
     rows per expert (experts nobody chose among them), the clamps, and the shared expert behind its gate."""
