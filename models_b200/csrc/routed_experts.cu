@@ -261,24 +261,35 @@ constexpr int kGroupTile = 128;
 
 __global__ void __launch_bounds__(1024)
 route_pad_kernel(const int* __restrict__ chosen, int entries, int experts, int* __restrict__ sorted, int* __restrict__ position,
-                 int* __restrict__ tile_group, int max_tiles) {
+                 int* __restrict__ tile_group, int max_tiles, int staged) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ int sort_shared[];
     int* counts = sort_shared;                 // [32][experts]
     int* totals = sort_shared + 32 * experts;  // [experts]
     int* starts = totals + experts;            // [experts + 1]
+    int* held = starts + experts + 1;          // [entries] if staged: every entry's expert (or -1), fetched once by all threads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < 32 * experts; i += blockDim.x) counts[i] = 0;
     for (int i = threadIdx.x; i < max_tiles * kGroupTile; i += blockDim.x) sorted[i] = -1;
+    if (staged) {
+#pragma unroll 8
+        for (int i = threadIdx.x; i < entries; i += blockDim.x) {  // (independent loads: many in flight per thread)
+            const int e = chosen[i];
+            held[i] = e < 0 || e >= experts ? -1 : e;
+        }
+    }
     __syncthreads();
+    auto expert_of = [&](int i) {
+        const int e = staged ? held[i] : chosen[i];
+        return e < 0 || e >= experts ? -1 : e;
+    };
     const int stretch = ((entries + 32 * 32 - 1) / (32 * 32)) * 32;
     const int first = warp * stretch, last = min(first + stretch, entries);
     int* mine = counts + warp * experts;
     for (int base = first; base < last; base += 32) {
         const int i = base + lane;
-        int e = i < last ? chosen[i] : -1;
-        if (e < 0 || e >= experts) e = -1;
+        const int e = i < last ? expert_of(i) : -1;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
         __syncwarp();
@@ -305,8 +316,7 @@ route_pad_kernel(const int* __restrict__ chosen, int entries, int experts, int* 
     __syncthreads();
     for (int base = first; base < last; base += 32) {
         const int i = base + lane;
-        int e = i < last ? chosen[i] : -1;
-        if (e < 0 || e >= experts) e = -1;
+        const int e = i < last ? expert_of(i) : -1;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         if (e >= 0) {
             const int at = starts[e] + mine[e] + __popc(same & ((1u << lane) - 1u));
@@ -318,7 +328,7 @@ route_pad_kernel(const int* __restrict__ chosen, int entries, int experts, int* 
         __syncwarp();
     }
     for (int i = first + lane; i < last; i += 32)  // (an entry whose expert does not exist reads row 0; its weight is what the router gave)
-        if (chosen[i] < 0 || chosen[i] >= experts) position[i] = 0;
+        if (expert_of(i) < 0) position[i] = 0;
 }
 
 // grid (max_tiles * kGroupTile); block 128.  out [row][K] = x [sorted[row] / top][K], zeros at rows that fill a tile up;
@@ -671,6 +681,33 @@ __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const 
     out[i] = sum;
 }
 
+// The same with four columns per thread (width a multiple of 4, rows on 16 bytes); every element's sum runs in the same order.
+template <typename T>
+__global__ void expert_combine_vec4_kernel(const float* __restrict__ slot_out, const float* __restrict__ weights,
+                                           const float* __restrict__ shared, const T* __restrict__ score, int score_stride,
+                                           float* __restrict__ out, size_t total4, int width, int top, const int* __restrict__ position) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int quads = width / 4;
+    const size_t t = i / quads;
+    const int c = (int)(i % quads) * 4;
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < top; ++s) {
+        const size_t row = position != nullptr ? (size_t)position[t * top + s] : t * top + s;
+        const float w = weights[t * top + s];
+        const float4 v = *reinterpret_cast<const float4*>(slot_out + row * width + c);
+        sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+    }
+    if (shared != nullptr) {
+        const float g = sigmoid(Num<T>::load(score + t * score_stride));
+        const float4 v = *reinterpret_cast<const float4*>(shared + t * width + c);
+        sum.x = fmaf(g, v.x, sum.x); sum.y = fmaf(g, v.y, sum.y); sum.z = fmaf(g, v.z, sum.z); sum.w = fmaf(g, v.w, sum.w);
+    }
+    *reinterpret_cast<float4*>(out + t * width + c) = sum;
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -735,8 +772,19 @@ MB_EXPORT int mb_route_pad(const int* chosen, int entries, int experts, int* sor
     if (entries <= 0) return 0;
     if (experts <= 0 || experts > kFastExperts) return fail("route_pad: %d experts (at most %d)", experts, kFastExperts);
     if (max_tiles < mb_route_pad_max_tiles(entries, experts)) return fail("route_pad: room for %d tiles, %d may be needed", max_tiles, mb_route_pad_max_tiles(entries, experts));
-    MB_LAUNCH("route_pad", route_pad_kernel, dim3(1), dim3(1024), (34 * (size_t)experts + 1) * sizeof(int), stream, true, chosen, entries,
-              experts, sorted, position, tile_group, max_tiles);
+    size_t smem = (34 * (size_t)experts + 1) * sizeof(int);
+    const int staged = smem + (size_t)entries * sizeof(int) <= 160 * 1024 ? 1 : 0;  // the entries' experts in shared memory, if they fit
+    if (staged) smem += (size_t)entries * sizeof(int);
+    if (smem > 48 * 1024) {
+        static size_t allowed = 0;  // (raised as needed; the attribute is per device context and function)
+        if (smem > allowed) {
+            if (cudaFuncSetAttribute(route_pad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024 + 48 * 1024) != cudaSuccess)
+                return fail("route_pad: cannot have %zu bytes of shared memory", smem);
+            allowed = 208 * 1024;
+        }
+    }
+    MB_LAUNCH("route_pad", route_pad_kernel, dim3(1), dim3(1024), smem, stream, true, chosen, entries, experts, sorted, position,
+              tile_group, max_tiles, staged);
     return 0;
 }
 
@@ -856,6 +904,18 @@ MB_EXPORT int mb_expert_combine(const float* slot_out, const float* weights, con
     if (tokens <= 0 || width <= 0) return 0;
     if (shared != nullptr && score == nullptr) return fail("expert_combine: a shared expert needs its gate scores");
     const size_t total = (size_t)tokens * width;
+    if (dtype != MB_F32 && dtype != MB_BF16) return fail("expert_combine: unknown dtype code %d", dtype);
+    if (width % 4 == 0 && !((uintptr_t)slot_out & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared & 15)) {
+        const size_t total4 = total / 4;
+        const dim3 grid4((unsigned)((total4 + 255) / 256));
+        if (dtype == MB_F32)
+            MB_LAUNCH("expert_combine", expert_combine_vec4_kernel<float>, grid4, dim3(256), 0, stream, true, slot_out, weights, shared,
+                      (const float*)score, score_stride, out, total4, width, top, position);
+        else
+            MB_LAUNCH("expert_combine", expert_combine_vec4_kernel<__nv_bfloat16>, grid4, dim3(256), 0, stream, true, slot_out, weights, shared,
+                      (const __nv_bfloat16*)score, score_stride, out, total4, width, top, position);
+        return 0;
+    }
     const dim3 grid((unsigned)((total + 255) / 256));
     if (dtype == MB_F32)
         MB_LAUNCH("expert_combine", expert_combine_kernel<float>, grid, dim3(256), 0, stream, true, slot_out, weights, shared, (const float*)score,
