@@ -1548,6 +1548,27 @@ def hyper_write(x: torch.Tensor, y: torch.Tensor, out_coefficients: torch.Tensor
                                  _stream()))
 
 
+def hyper_write_read_norm(x: torch.Tensor, y: torch.Tensor, out_coefficients: torch.Tensor, mix: torch.Tensor, coefficients: torch.Tensor,
+                          gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """`hyper_write(x, y, out_coefficients, mix)` and then `hyper_read_norm(x, coefficients, gain, eps, out_dtype)` in one pass
+    over the copies (the same bits as the two calls); y float32 [tokens, width]."""
+    _cuda(x, y, out_coefficients, mix, coefficients, gain)
+    _columns(y, "y")
+    width = y.shape[1]
+    streams = _streams_of(x, width, "hyper_write_read_norm")
+    if y.shape[0] != x.shape[0] or y.dtype != torch.float32 or gain.numel() != width:
+        raise KernelError(f"hyper_write_read_norm: y {tuple(y.shape)} {y.dtype} does not fit the streams {tuple(x.shape)}")
+    for name, t, count in (("out_coefficients", out_coefficients, streams), ("mix", mix, streams * streams), ("coefficients", coefficients, streams),
+                           ("gain", gain, width)):
+        if t.dtype != torch.float32 or t.numel() != count or not t.is_contiguous():
+            raise KernelError(f"hyper_write_read_norm: {name} must be contiguous float32 of {count} elements")
+    out = torch.empty((x.shape[0], width), dtype=out_dtype, device=x.device)
+    lib = hyper_streams_library()
+    _run(lib, lib.mb_hyper_write_read_norm(_p(x), _p(y), y.stride(0), _p(out_coefficients), _p(mix), _p(coefficients), _p(gain), _p(out),
+                                           _code(out_dtype), x.shape[0], width, streams, ctypes.c_float(eps), _stream()))
+    return out
+
+
 def hyper_max_streams() -> int:
     return hyper_streams_library().mb_hyper_max_streams()
 

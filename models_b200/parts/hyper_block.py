@@ -6,8 +6,9 @@ mix [streams, streams] (indexed [from, to]):
 
     u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t at once, from the old copies)
 
-Reading (the weighted sum and the RMS norm) is one kernel, writing (the mixing and the addition) another; y reaches the
-writing kernel as the float32 sums of the sublayer's last product, in both modes.  With `streams` 0 there is one stream
+Reading (the weighted sum and the RMS norm) is one kernel, writing (the mixing and the addition) another, and the mixer's
+writing with the feed-forward's reading a third that passes over the copies once; y reaches the writing kernel as the
+float32 sums of the sublayer's last product, in both modes.  With `streams` 0 there is one stream
 and no such numbers: x += sublayer(norm(x)), the addition riding in the last product where its kernel takes it.
 
 A sublayer is a split part (a first product, something in between, a last product) or a part that offers
@@ -98,6 +99,17 @@ class HyperBlock(Part):
     def forward(self, x: torch.Tensor, pending, batch, run: RunContext):
         if as_delta(pending) is not None:
             raise RuntimeError("a block over several streams takes no pending delta: the block before it must have added its own")
+        if self.streams and self.feed_forward is not None:
+            # the mixer's result goes into the copies and the feed-forward's reading comes out of them in one pass
+            dtype = self.runtime.compute_dtype
+            read, out, mix = self.connections["mixer"]
+            xn = ops.hyper_read_norm(x, read, self.mixer_norm.weight, self.mixer_norm.spec.eps, dtype)
+            y = self._result(self.mixer, xn, batch, run)
+            norm = self.feed_forward_norm
+            read, out_ff, mix_ff = self.connections["feed_forward"]
+            xn = ops.hyper_write_read_norm(x, y, out, mix, read, norm.weight, norm.spec.eps, dtype)
+            ops.hyper_write(x, self._result(self.feed_forward, xn, batch, run), out_ff, mix_ff)
+            return None
         self._sublayer(x, "mixer", self.mixer_norm, self.mixer, batch, run)
         if self.feed_forward is not None:
             self._sublayer(x, "feed_forward", self.feed_forward_norm, self.feed_forward, batch, run)

@@ -265,6 +265,16 @@ def test_reading_and_writing_the_streams(cuda_device, streams, width, tokens, dt
     assert scaled_error(ops.stream_sum(xd, width), want.sum(1)) < 2e-6
     copies = ops.stream_copies(dev(y), streams).reshape(tokens, streams, width)
     assert all(torch.equal(copies[:, s], dev(y)) for s in range(streams))
+    # writing and the next reading in one pass: the oracle's numbers, and the same bits as the two kernels one after the other
+    read2 = torch.randn(streams, generator=g, dtype=F)
+    y32 = dev(torch.randn(tokens, width, generator=g, dtype=F))
+    one, two = dev(x.reshape(tokens, streams * width)), dev(x.reshape(tokens, streams * width))
+    got = ops.hyper_write_read_norm(one, y32, dev(out), dev(mix), dev(read2), dev(gain), 1e-5, dtype)
+    ops.hyper_write(two, y32, dev(out), dev(mix))
+    assert torch.equal(one, two) and torch.equal(got, ops.hyper_read_norm(two, dev(read2), dev(gain), 1e-5, dtype))
+    want = torch.einsum("sr,tsd->trd", mix.float().double(), x.float().double()) + out.float().double()[None, :, None] * y32.double().cpu()[:, None, :]
+    assert scaled_error(one.reshape(tokens, streams, width), want) < 2e-6
+    assert scaled_error(got, pk.rms_norm(torch.einsum("s,tsd->td", read2.float().double(), want), gain, 1e-5)) < KERNEL_TOLERANCE[dtype]
 
 
 @pytest.mark.parametrize("experts,top,width,ff,tokens", [(4, 2, 64, 40, 70), (7, 3, 200, 136, 333), (16, 1, 128, 264, 500), (3, 3, 72, 8, 129),
