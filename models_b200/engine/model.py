@@ -95,6 +95,10 @@ class DecoderModel:
                 following = self.blocks[schedule[index + 1].layer] if index + 1 < len(schedule) else None
                 next_norm = getattr(following, "mixer_norm", None) if following is not None else self.final_norm
                 pending = block.forward(x, pending, batch, run, next_norm)
+            elif getattr(block, "takes_next_block", False):
+                # the block that reads the streams after this run (none after the last one): its reading may ride in this one's writing
+                following = self.blocks[schedule[index + 1].layer] if index + 1 < len(schedule) else None
+                pending = block.forward(x, pending, batch, run, following)
             else:
                 pending = block.forward(x, as_delta(pending), batch, run)
             if self.observer is not None:

@@ -99,10 +99,20 @@ class Prenormed:
         return self.ssq, self.count, self.width, self.eps
 
 
+@dataclass
+class StreamsRead:
+    """What a block over several copies of the stream may hand on: the copies are up to date, and `rows` is what the
+    block `reader` reads through its first norm (the weighted sum of the copies, normalised), taken while the copies
+    were being written."""
+
+    rows: torch.Tensor
+    reader: object
+
+
 def as_delta(pending):
-    """The delta that is still to be added into the residual stream, or None (also for a Prenormed: the
-    stream it belongs to is up to date)."""
-    return None if isinstance(pending, Prenormed) else pending
+    """The delta that is still to be added into the residual stream, or None (also for a Prenormed or a StreamsRead:
+    the stream they belong to is up to date)."""
+    return None if isinstance(pending, (Prenormed, StreamsRead)) else pending
 
 
 class Part:

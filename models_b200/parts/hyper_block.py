@@ -6,8 +6,8 @@ mix [streams, streams] (indexed [from, to]):
 
     u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t at once, from the old copies)
 
-Reading (the weighted sum and the RMS norm) is one kernel, writing (the mixing and the addition) another, and the mixer's
-writing with the feed-forward's reading a third that passes over the copies once; y reaches the writing kernel as the
+Reading (the weighted sum and the RMS norm) is one kernel, writing (the mixing and the addition) another, and a writing
+with the reading that follows it (the feed-forward's, or the next block's) a third that passes over the copies once; y reaches the writing kernel as the
 float32 sums of the sublayer's last product, in both modes.  With `streams` 0 there is one stream
 and no such numbers: x += sublayer(norm(x)), the addition riding in the last product where its kernel takes it.
 
@@ -21,12 +21,14 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import ParamRequest
-from .base import Part, RunContext, as_delta
+from .base import Part, RunContext, StreamsRead, as_delta
 from .linear import add_linear, linear
 from .registry import build_part, register_part
 
 
 class HyperBlock(Part):
+    takes_next_block = True  # `forward` is told which block runs next
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
@@ -96,23 +98,36 @@ class HyperBlock(Part):
         else:
             add_linear(x, self._middle(part, xn, batch, run), part.output_matrix())
 
-    def forward(self, x: torch.Tensor, pending, batch, run: RunContext):
+    def forward(self, x: torch.Tensor, pending, batch, run: RunContext, following=None):
+        """`pending`: None, or a StreamsRead that the block before took for this one.  `following`: the block that runs next."""
+        if isinstance(pending, StreamsRead) and pending.reader is not self:
+            pending = None  # (somebody else's reading: the copies are up to date all the same)
         if as_delta(pending) is not None:
             raise RuntimeError("a block over several streams takes no pending delta: the block before it must have added its own")
-        if self.streams and self.feed_forward is not None:
-            # the mixer's result goes into the copies and the feed-forward's reading comes out of them in one pass
-            dtype = self.runtime.compute_dtype
-            read, out, mix = self.connections["mixer"]
+        if not self.streams:
+            self._sublayer(x, "mixer", self.mixer_norm, self.mixer, batch, run)
+            if self.feed_forward is not None:
+                self._sublayer(x, "feed_forward", self.feed_forward_norm, self.feed_forward, batch, run)
+            return None
+        # Every writing but the model's last passes over the copies together with the reading that follows it (the
+        # feed-forward's, or the next block's mixer's): one kernel, the same bits as the two.
+        dtype = self.runtime.compute_dtype
+        read, out, mix = self.connections["mixer"]
+        if isinstance(pending, StreamsRead):
+            xn = pending.rows
+        else:
             xn = ops.hyper_read_norm(x, read, self.mixer_norm.weight, self.mixer_norm.spec.eps, dtype)
-            y = self._result(self.mixer, xn, batch, run)
+        y = self._result(self.mixer, xn, batch, run)
+        if self.feed_forward is not None:
             norm = self.feed_forward_norm
             read, out_ff, mix_ff = self.connections["feed_forward"]
             xn = ops.hyper_write_read_norm(x, y, out, mix, read, norm.weight, norm.spec.eps, dtype)
-            ops.hyper_write(x, self._result(self.feed_forward, xn, batch, run), out_ff, mix_ff)
-            return None
-        self._sublayer(x, "mixer", self.mixer_norm, self.mixer, batch, run)
-        if self.feed_forward is not None:
-            self._sublayer(x, "feed_forward", self.feed_forward_norm, self.feed_forward, batch, run)
+            y, out, mix = self._result(self.feed_forward, xn, batch, run), out_ff, mix_ff
+        if isinstance(following, HyperBlock) and following.streams == self.streams:
+            norm = following.mixer_norm
+            rows = ops.hyper_write_read_norm(x, y, out, mix, following.connections["mixer"][0], norm.weight, norm.spec.eps, dtype)
+            return StreamsRead(rows, following)
+        ops.hyper_write(x, y, out, mix)
         return None
 
 
