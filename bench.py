@@ -766,6 +766,8 @@ def kivezen_kernels(z, peak, prompt=2048, batch=8, context=1536):
         out[f"{name}_streams_read_norm"] = rated(us, moved=rows * W * (4 * S + 2))
         us = time_kernel(lambda: ops.hyper_write(streams, delta, write, mix))
         out[f"{name}_streams_write"] = rated(us, moved=rows * W * (8 * S + 4))
+        us = time_kernel(lambda: ops.hyper_write_read_norm(streams, delta, write, mix, read, ones, 1e-6, bf))  # as the blocks run them
+        out[f"{name}_streams_write_and_read_norm"] = rated(us, moved=rows * W * (8 * S + 4 + 2))
         one = torch.randn((rows, W), device=dev)
         us = time_kernel(lambda: ops.add_rmsnorm(one, None, ones, 1e-6, bf))
         out[f"{name}_rmsnorm_llama"] = rated(us, moved=rows * W * 6)
