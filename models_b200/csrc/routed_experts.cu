@@ -724,8 +724,11 @@ MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, in
     if (one > 200 * 1024) return fail("router_topk: a row of %d and %d logits exceed a block's shared memory", width, experts);
     const size_t unit = dtype == MB_F32 ? 32 : 16, element = dtype == MB_F32 ? 4 : 2;
     const bool vector = width % 8 == 0 && ((size_t)x_stride * element) % unit == 0 && !((uintptr_t)x % unit) && !((uintptr_t)router % unit);
-    constexpr int kTogether = 4;  // tokens of a prompt that share what a block loads of the router
+    // tokens of a prompt that share what a block loads of the router: four, or eight where blocks of four would not all be
+    // resident at once (the kernel is bound by a block's latency, so a second wave of blocks doubles its time)
+    constexpr int kTogether = 4, kMany = 8;
     const bool together = vector && tokens >= 64 * kTogether && kTogether * one <= 200 * 1024;
+    const bool many = together && (tokens + kTogether - 1) / kTogether > 2 * 148 && kMany * one <= 72 * 1024;
 #define MB_ROUTER(T, VECTOR, TOKENS)                                                                                                  \
     do {                                                                                                                              \
         const size_t smem = TOKENS * one;                                                                                             \
@@ -735,9 +738,9 @@ MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, in
                   true, (const T*)x, x_stride, (const T*)router, chosen, weights, tokens, width, experts, top);                       \
     } while (0)
     if (dtype == MB_F32) {
-        if (together) MB_ROUTER(float, true, kTogether); else if (vector) MB_ROUTER(float, true, 1); else MB_ROUTER(float, false, 1);
+        if (many) MB_ROUTER(float, true, kMany); else if (together) MB_ROUTER(float, true, kTogether); else if (vector) MB_ROUTER(float, true, 1); else MB_ROUTER(float, false, 1);
     } else if (dtype == MB_BF16) {
-        if (together) MB_ROUTER(__nv_bfloat16, true, kTogether); else if (vector) MB_ROUTER(__nv_bfloat16, true, 1); else MB_ROUTER(__nv_bfloat16, false, 1);
+        if (many) MB_ROUTER(__nv_bfloat16, true, kMany); else if (together) MB_ROUTER(__nv_bfloat16, true, kTogether); else if (vector) MB_ROUTER(__nv_bfloat16, true, 1); else MB_ROUTER(__nv_bfloat16, false, 1);
     } else {
         return fail("router_topk: unknown dtype code %d", dtype);
     }
