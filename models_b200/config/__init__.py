@@ -1,6 +1,7 @@
 from .kabanex import KabanexConfig
 from .llama import ConfigError, LlamaConfig, RopeScalingConfig
 from .lovurax import LovuraxConfig
+from .rolevik import RolevikConfig
 from .registry import (
     config_from_dict,
     known_architectures,

@@ -15,6 +15,7 @@ from .kabanex import ARCHITECTURE as KABANEX, KabanexConfig
 from .kivezen import ARCHITECTURE as KIVEZEN, KivezenConfig
 from .llama import ConfigError, LlamaConfig
 from .lovurax import ARCHITECTURE as LOVURAX, LovuraxConfig
+from .rolevik import ARCHITECTURE as ROLEVIK, RolevikConfig
 
 # name -> callable(raw config.json dict) -> object with .model_spec()
 _ARCHITECTURES: Dict[str, Callable[[Mapping[str, Any]], Any]] = {}
@@ -68,3 +69,4 @@ register_architecture("LlamaForCausalLM", LlamaConfig.from_dict)
 register_architecture(KABANEX, KabanexConfig.from_dict)
 register_architecture(LOVURAX, LovuraxConfig.from_dict)
 register_architecture(KIVEZEN, KivezenConfig.from_dict)
+register_architecture(ROLEVIK, RolevikConfig.from_dict)

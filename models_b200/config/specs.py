@@ -77,12 +77,13 @@ class AttentionSpec:
 @dataclass(frozen=True)
 class LayerNormSpec:
     """(x - mean) / sqrt(variance + eps) * weight + bias over the last axis; the variance is the mean of
-    the squared deviations from the mean."""
+    the squared deviations from the mean.  `bias` False: there is no bias tensor."""
 
     size: int
     eps: float
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
     kind: str = "layernorm"
+    bias: bool = True
 
 
 @dataclass(frozen=True)
@@ -371,11 +372,13 @@ class CappedAttentionSpec:
 @dataclass(frozen=True)
 class ClampedExpertSpec:
     """One gated feed-forward with clamped branches: g = min(gate . x, limit), u = clamp(up . x, -limit, limit),
-    down . (g * sigmoid(swish_slope * g) * (u + 1)); no biases."""
+    down . (g * sigmoid(swish_slope * g) * (u + up_offset)); no biases.  limit = +inf, swish_slope 1 and up_offset 0 make the
+    plain gated form down . (silu(gate . x) * (up . x))."""
 
     intermediate_size: int
     limit: float
     swish_slope: float
+    up_offset: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -393,6 +396,19 @@ class RoutedFeedForwardSpec:
     shared: Optional[ClampedExpertSpec]
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
     kind: str = "routed"
+    # Variations.  `rule` "scored": the scores s = softmax(z) are taken over ALL router outputs; the choice runs on
+    # s + correction (a tensor of one number per router output, `weights["correction"]`, when `correction` is set); the outputs
+    # form `groups` equal groups of neighbours, a group counts by its largest choice score, and only outputs of the
+    # `keep_groups` best groups can be chosen; the weights are `weight_scale` times the chosen outputs' s, not renormalised.
+    # `identity_experts` n: the router has num_experts + n outputs, the last n of which stand for experts without tensors
+    # whose result is their input.  `shared_gated` False: the shared expert is added as it is (no `shared_gate_score` tensor).
+    rule: str = "top_logits"
+    correction: bool = False
+    groups: int = 1
+    keep_groups: int = 1
+    weight_scale: float = 1.0
+    identity_experts: int = 0
+    shared_gated: bool = True
 
 
 @dataclass(frozen=True)
@@ -410,3 +426,92 @@ class HyperBlockSpec:
     streams: int
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
     kind: str = "prenorm_hyper"
+
+
+@dataclass(frozen=True)
+class ChunkedAttentionSpec:
+    """Causal grouped-query softmax attention whose projections are normalised as a whole.  q, k and v have biases when
+    `bias` is set; with `projection_norm` q (all heads side by side) passes ONE RMS norm with a gain of that size and eps `eps`,
+    and so does k, before the heads are split and rotated (`position`, or None).  score = scale * q.k.  `chunk` n: query i sees
+    key j <= i only if floor(i / n) = floor(j / n), chunks counted from position 0 of the sequence (None: every earlier key).
+    Keys have `head_dim` coordinates, values `value_dim`."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    position: Optional[RopeSpec]
+    chunk: Optional[int]
+    bias: bool
+    projection_norm: bool
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "chunked_attention"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule.  q and k (`num_kv_heads` heads of `head_dim`) and v (`num_heads` heads of `value_dim`) pass a short
+    causal convolution over time per channel (`conv_taps` weights, the last one meeting the current token, zeros before the
+    sequence's start) and a silu; q and k become unit vectors x / sqrt(sum x^2 + unit_eps), q times head_dim^-1/2;
+    beta = sigmoid(b . xn) and g = exp(-exp(A_log) * softplus(a . xn + dt_bias)), one number per head; per head with a float32
+    state S [head_dim, value_dim] that starts at zero: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Every
+    head's o is divided by its root mean square (eps `eps`), multiplied by a gain of value_dim numbers the heads share and by
+    silu(gate . xn); then the output matrix.  The last conv_taps - 1 inputs of the convolutions are part of the state."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    unit_eps: float
+    eps: float
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class RglruSpec:
+    """A recurrent block around a real-gated linear recurrent unit.  Two branches of `width` channels: y = gelu_tanh(Wy . xn + by)
+    and u = conv(Wx . xn + bx), a short causal convolution per channel with a bias.  The channels form `blocks` equal blocks;
+    in block b, r = sigmoid(Ra[b] u_b + ra_b) and i = sigmoid(Ri[b] u_b + ri_b) with square matrices; log a = -rate * r *
+    softplus(lambda), S_t = a S_(t-1) + sqrt(1 - a^2) * i * u with a float32 state that starts at zero; result Wo . (S * y).
+    The last conv_taps - 1 inputs of the convolution are part of the state."""
+
+    hidden_size: int
+    width: int
+    blocks: int
+    conv_taps: int
+    rate: float
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "rglru"
+
+
+@dataclass(frozen=True)
+class NormedPairSpec:
+    """Two mixers that read the same rows, each with an output matrix of its own; the result is the mean of the two results
+    after an RMS norm each over the model's width (eps `eps`, gains `weights["left"]` and `weights["right"]`)."""
+
+    left: object
+    right: object
+    hidden_size: int
+    eps: float
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "normed_pair"
+
+
+@dataclass(frozen=True)
+class OutputNormBlockSpec:
+    """A layer whose norms sit on the sublayers' RESULTS: x += mixer_scale * mixer_norm(mixer(x)); then, if the layer has a
+    feed-forward, x += feed_forward_scale * feed_forward_norm(feed_forward(x)).  The sublayers read x itself; the scales are
+    tensors of the model's width (`weights`: mixer_scale, feed_forward_scale), multiplied element by element."""
+
+    mixer: object
+    feed_forward: Optional[object]
+    mixer_norm: object
+    feed_forward_norm: Optional[object]
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "output_norm"

@@ -367,7 +367,68 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
     Out* out_row = out + (size_t)blockIdx.x * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
-        Num<Out>::store(out_row + i, (row[i] - mean) * inv * weight[i] + bias[i]);
+        Num<Out>::store(out_row + i, (row[i] - mean) * inv * weight[i] + (bias != nullptr ? bias[i] : 0.0f));
+}
+
+// One block per row of the float32 stream.  The sublayer's result y is `a`, or -- with a second result `b` -- the mean of
+// the two after an RMS norm each: y = 1/2 (a / rms(a) * gain_a + b / rms(b) * gain_b), rms(v) = sqrt(mean(v^2) + eps).
+// Then x += scale * LN(y), LN(y) = (y - mean) / sqrt(var + eps) * weight with var the mean of the squared deviations (two
+// walks), and, where `copy` is given, the new row of x is stored there in the storage type (what the next sublayer's
+// products read).  The row lives in shared memory (width floats).
+template <typename Out>
+__global__ void outnorm_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                                   const float* __restrict__ gain_a, const float* __restrict__ gain_b,
+                                   const float* __restrict__ weight, const float* __restrict__ scale, Out* __restrict__ copy,
+                                   int width, float eps) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float scratch[32];
+    extern __shared__ float kept[];
+    const size_t at = (size_t)blockIdx.x * width;
+    float sum = 0.0f;
+    if (b != nullptr) {
+        float sa = 0.0f, sb = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float va = a[at + i], vb = b[at + i];
+            sa = fmaf(va, va, sa);
+            sb = fmaf(vb, vb, sb);
+        }
+        const float ia = 1.0f / sqrtf(block_sum(sa, scratch) / (float)width + eps);
+        const float ib = 1.0f / sqrtf(block_sum(sb, scratch) / (float)width + eps);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float y = 0.5f * (a[at + i] * ia * gain_a[i] + b[at + i] * ib * gain_b[i]);
+            kept[i] = y;
+            sum += y;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) sum += (kept[i] = a[at + i]);
+    }
+    if (weight == nullptr) {  // no layer norm and no addition: x = y
+        __syncthreads();
+        for (int i = threadIdx.x; i < width; i += blockDim.x) x[at + i] = kept[i];
+        return;
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;  // (its barriers order the writes of `kept` before the reads)
+    float squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = kept[i] - mean;
+        squares = fmaf(d, d, squares);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = x[at + i] + scale[i] * ((kept[i] - mean) * inv * weight[i]);
+        x[at + i] = v;
+        if (copy != nullptr) Num<Out>::store(copy + at + i, v);
+    }
+}
+
+// dst = src in another storage type, element by element.
+template <typename Out>
+__global__ void store_rows_kernel(const float* __restrict__ src, Out* __restrict__ dst, size_t total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        Num<Out>::store(dst + i, src[i]);
 }
 
 // Eight elements a thread (columns and strides are multiples of 8 and the slices start on 16 bytes; 32 for float).
@@ -599,6 +660,41 @@ MB_EXPORT int mb_layernorm(const float* x, const float* weight, const float* bia
     else
         return fail("layernorm: unknown dtype code %d", out_dtype);
     return check_launch("layernorm");
+}
+
+// x [rows, width] += scale * LN(y) with y = a, or the mean of the RMS-normed a and b (see the kernel); `copy` (or null)
+// receives the new rows in `copy_dtype`.  With `weight` null nothing is normed or added: x = y.
+MB_EXPORT int mb_outnorm_add(float* x, const float* a, const float* b, const float* gain_a, const float* gain_b,
+                             const float* weight, const float* scale, void* copy, int copy_dtype, int rows, int width, float eps,
+                             cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    if (width > 12000) return fail("outnorm_add: rows of %d floats exceed the 12000 a block keeps", width);
+    if (b != nullptr && (gain_a == nullptr || gain_b == nullptr)) return fail("outnorm_add: two results need two gains");
+    const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+    const size_t smem = sizeof(float) * (size_t)width;
+    if (copy == nullptr || copy_dtype == MB_F32)
+        MB_LAUNCH("elementwise", outnorm_add_kernel<float>, dim3(rows), dim3(threads), smem, stream, true, x, a, b, gain_a, gain_b,
+                  weight, scale, (float*)copy, width, eps);
+    else if (copy_dtype == MB_BF16)
+        MB_LAUNCH("elementwise", outnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream, true, x, a, b, gain_a,
+                  gain_b, weight, scale, (__nv_bfloat16*)copy, width, eps);
+    else
+        return fail("outnorm_add: unknown dtype code %d", copy_dtype);
+    return check_launch("outnorm_add");
+}
+
+// dst = src (float) stored as `dtype`.
+MB_EXPORT int mb_store_rows(const float* src, void* dst, int dtype, size_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    const size_t blocks = (total + 255) / 256;
+    const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
+    if (dtype == MB_F32)
+        MB_LAUNCH("elementwise", store_rows_kernel<float>, dim3(grid), dim3(256), 0, stream, true, src, (float*)dst, total);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("elementwise", store_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true, src, (__nv_bfloat16*)dst, total);
+    else
+        return fail("store_rows: unknown dtype code %d", dtype);
+    return check_launch("store_rows");
 }
 
 // dst[r, c] = scale * act(src[r, c]) for [rows, cols] column slices with row strides (in elements); activation: MB_ACT_*.

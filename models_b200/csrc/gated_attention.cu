@@ -11,6 +11,8 @@
 // bound, score <- cap * tanh(score / cap), applied after everything else; a sink, one more term of score 0 that has no
 // value in the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)); and values that were stored rotated by their
 // own position (pairs 2m, 2m + 1): the head's sum is then turned back by the query's position before any gate.
+// Visibility may be cut into blocks: with `block` n > 0, query i sees key j <= i only if floor(i / n) = floor(j / n)
+// (blocks of n positions counted from position 0 of the sequence).
 //
 // Keys have head_dim coordinates and values value_dim; the value rows may lie in a pool of their own or be the
 // first value_dim coordinates of the key rows (a cache that keeps one row per position, read as key and as value).
@@ -37,7 +39,11 @@ struct ScoreExtras {
     int sink;                 // != 0: the softmax's denominator has one more term of score 0
     const float* turn_cos;    // [positions][value_dim / 2] with turn_sin: the result's pairs (2m, 2m + 1) are turned by
     const float* turn_sin;    // minus the query's position; null: the result stays as it is
+    int block;                // n > 0: a query sees only the keys of its own block of n positions; 0: every earlier key
 };
+
+// the first position a query at `pos` sees
+__device__ __forceinline__ int lowest_visible(int pos, int block) { return block > 0 ? (pos / block) * block : 0; }
 
 __device__ __forceinline__ float bounded(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
 
@@ -265,6 +271,76 @@ __global__ void norm_store_kernel(T* __restrict__ q, int q_stride, const T* __re
     }
 }
 
+// grid (tokens); block 128 or 256.  Query and key projections that are normalised as a WHOLE, all heads at once:
+//   q <- (q + q_bias) / rms(q + q_bias) * q_gain over the row of heads * head_dim numbers (rms(x) = sqrt(mean(x^2) + eps);
+//   a null gain: that side is not normalised), the same for k over its kv_heads * head_dim numbers; then every head's first
+//   `rotation.dim` coordinates are rotated by the token's position (tables as above); q is written back in place, k goes into
+//   the cache, and v (+ v_bias) into its pool as it is.  Biases may be null.
+// shared: (heads + kv_heads) * head_dim floats (the two rows, so that a pair's partner is read after the norm).
+template <typename T>
+__global__ void project_norm_rotate_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                                                 const T* __restrict__ v, int v_stride, const float* __restrict__ q_bias,
+                                                 const float* __restrict__ k_bias, const float* __restrict__ v_bias,
+                                                 const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                                                 const int* __restrict__ positions, Rotation rotation, T* __restrict__ k_pool,
+                                                 T* __restrict__ v_pool, const int* __restrict__ slot_mapping, int heads, int kv_heads,
+                                                 int head_dim, int value_dim, int page_size) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float scratch[32];
+    extern __shared__ float both_rows[];
+    const int token = blockIdx.x;
+    const int q_width = heads * head_dim, k_width = kv_heads * head_dim;
+    float* q_row = both_rows;
+    float* k_row = both_rows + q_width;
+    const int pos = positions[token];
+    const int slot = slot_mapping[token];
+    const size_t page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+    float q_squares = 0.0f, k_squares = 0.0f;
+    for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
+        const float x = Num<T>::load(q + (size_t)token * q_stride + i) + (q_bias != nullptr ? q_bias[i] : 0.0f);
+        q_row[i] = x;
+        q_squares = fmaf(x, x, q_squares);
+    }
+    for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
+        const float x = Num<T>::load(k + (size_t)token * k_stride + i) + (k_bias != nullptr ? k_bias[i] : 0.0f);
+        k_row[i] = x;
+        k_squares = fmaf(x, x, k_squares);
+    }
+    const float q_factor = q_gain != nullptr ? 1.0f / sqrtf(block_sum(q_squares, scratch) / (float)q_width + eps) : 1.0f;
+    const float k_factor = k_gain != nullptr ? 1.0f / sqrtf(block_sum(k_squares, scratch) / (float)k_width + eps) : 1.0f;
+    __syncthreads();
+    const int turning = rotation.dim, half = rotation.dim / 2;
+    const float* cos_row = turning > 0 ? rotation.cos + (size_t)pos * half : nullptr;
+    const float* sin_row = turning > 0 ? rotation.sin + (size_t)pos * half : nullptr;
+    for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
+        const bool is_query = i < q_width;
+        const int at = is_query ? i : i - q_width;
+        const int head = at / head_dim, d = at % head_dim;
+        const float* row = is_query ? q_row : k_row;
+        const float* gain = is_query ? q_gain : k_gain;
+        const float factor = is_query ? q_factor : k_factor;
+        float x = row[at] * factor * (gain != nullptr ? gain[at] : 1.0f);
+        if (d < turning) {
+            const bool first = rotation.interleaved ? (d & 1) == 0 : d < half;
+            const int pair = rotation.interleaved ? d >> 1 : (d < half ? d : d - half);
+            const int other = at - d + (rotation.interleaved ? d ^ 1 : (d < half ? d + half : d - half));
+            const float partner = row[other] * factor * (gain != nullptr ? gain[other] : 1.0f);
+            x = first ? x * cos_row[pair] - partner * sin_row[pair] : x * cos_row[pair] + partner * sin_row[pair];
+        }
+        if (is_query)
+            Num<T>::store(q + (size_t)token * q_stride + at, x);
+        else if (slot >= 0)
+            Num<T>::store(k_pool + ((page * kv_heads + head) * page_size + offset) * head_dim + d, x);
+    }
+    if (slot < 0 || value_dim <= 0) return;
+    for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+        const int head = i / value_dim, d = i % value_dim;
+        const float x = Num<T>::load(v + (size_t)token * v_stride + i) + (v_bias != nullptr ? v_bias[i] : 0.0f);
+        Num<T>::store(v_pool + ((page * kv_heads + head) * page_size + offset) * value_dim + d, x);
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q_shared, const T* __restrict__ k_row, int head_dim,
                                          bool vector_ok) {
@@ -322,12 +398,13 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float running_max = kSoftmax && extras.sink ? 0.0f : -CUDART_INF_F, running_sum = kSoftmax && extras.sink ? 1.0f : 0.0f;
     const int* table = block_table + (size_t)seq * max_blocks;
 
-    for (int chunk = 0; chunk <= pos; chunk += 32) {
+    const int lowest = lowest_visible(pos, extras.block);
+    for (int chunk = lowest & ~31; chunk <= pos; chunk += 32) {  // (the first chunk holds `lowest`: every chunk has a visible key)
         // page_size is a multiple of 32, so a chunk of 32 positions lies in one page
         const size_t page = table[chunk / page_size];
         const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
         const int p = chunk + lane;
-        const bool visible = p <= pos;
+        const bool visible = p <= pos && p >= lowest;
         float score = -CUDART_INF_F;
         if (visible)
             score = bounded(dot_row<T>(q_shared, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale - slope * (float)(pos - p) + bias,
@@ -408,8 +485,9 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
     const int head0 = kv_head * group + part * kGroup;
     const int count = min(kGroup, group - part * kGroup);
     const int pos = kv_lens[seq] - 1;
-    const int begin = split * span * page_size;
-    const int end = min(pos + 1, begin + span * page_size);
+    const int lowest = lowest_visible(pos, extras.block);
+    const int end = min(pos + 1, (split + 1) * span * page_size);
+    const int begin = max(split * span * page_size, lowest & ~31);  // (the chunk of 32 that holds `lowest`: every chunk has a visible key)
     const int stride = 2 + value_dim;
     float* q_shared = decode_shared;
     float* meet = decode_shared + kGroup * head_dim;  // [warp][kGroup][stride]
@@ -449,7 +527,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         const size_t page = table[chunk / page_size];
         const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
         const int p = chunk + lane;
-        const bool visible = p < end;
+        const bool visible = p < end && p >= lowest;
         if (staged) {
             __syncwarp();  // the lanes are done with the chunk before
             const unsigned char* k_src = reinterpret_cast<const unsigned char*>(k_pool + base * head_dim);
@@ -888,12 +966,12 @@ MB_EXPORT int mb_gated_attention_rows(const void* q, int q_stride, void* out, in
                                       const int* kv_lens, const float* head_bias, const void* gate, int gate_stride, int gate_kind,
                                       int sequences, int max_q_len, int heads, int kv_heads, int head_dim, int value_dim,
                                       int page_size, int softmax, float scale, float slope_exponent, const float* head_scale,
-                                      float softcap, int sink, const float* turn_cos, const float* turn_sin, cudaStream_t stream) {
+                                      float softcap, int sink, const float* turn_cos, const float* turn_sin, int block, cudaStream_t stream) {
     if (sequences <= 0 || max_q_len <= 0) return 0;
     if ((turn_cos == nullptr) != (turn_sin == nullptr) || (turn_cos != nullptr && value_dim % 2))
         return fail("gated_attention_rows: turning the result back needs both tables and an even value_dim (%d)", value_dim);
     if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_rows: softcap %g, a sink without a softmax", softcap);
-    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin, block};
     if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_rows: head_dim %d is outside 1..2048", head_dim);
     if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
         return fail("gated_attention_rows: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
@@ -971,12 +1049,12 @@ MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, 
                                         int sequences, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
                                         int softmax, float scale, float slope_exponent, int splits, int span, float* partial,
                                         const float* head_scale, float softcap, int sink, const float* turn_cos,
-                                        const float* turn_sin, cudaStream_t stream) {
+                                        const float* turn_sin, int block, cudaStream_t stream) {
     if (sequences <= 0) return 0;
     if ((turn_cos == nullptr) != (turn_sin == nullptr) || (turn_cos != nullptr && value_dim % 2))
         return fail("gated_attention_decode: turning the result back needs both tables and an even value_dim (%d)", value_dim);
     if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_decode: softcap %g, a sink without a softmax", softcap);
-    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin, block};
     if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_decode: head_dim %d is outside 1..2048", head_dim);
     if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
         return fail("gated_attention_decode: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
@@ -1039,4 +1117,32 @@ MB_EXPORT int mb_head_linear(const void* in, int in_stride, const void* w, void*
         return fail("head_linear: unknown dtype code %d", dtype);
     }
     return check_launch("head_linear");
+}
+
+// q (in place), k and v rows of one storage type (row strides in elements); biases and gains float or null; cos/sin tables
+// [positions][rotary_dim / 2] (rotary_dim 0: no rotation).
+MB_EXPORT int mb_project_norm_rotate_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                                           const float* q_bias, const float* k_bias, const float* v_bias, const float* q_gain,
+                                           const float* k_gain, float eps, const int* positions, const float* cos, const float* sin,
+                                           int rotary_dim, int interleaved, void* k_pool, void* v_pool, const int* slot_mapping,
+                                           int tokens, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
+                                           cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim) return fail("project_norm_rotate_store: rotary_dim %d of heads of %d", rotary_dim, head_dim);
+    const size_t smem = sizeof(float) * (size_t)(heads + kv_heads) * head_dim;
+    if (smem > 40 * 1024) return fail("project_norm_rotate_store: rows of %d numbers exceed the 10240 a block keeps", (heads + kv_heads) * head_dim);
+    const Rotation rotation{cos, sin, rotary_dim, interleaved, 0, nullptr, nullptr, 0};
+    const int threads = (heads + kv_heads) * head_dim >= 1024 ? 256 : 128;
+    if (dtype == MB_F32)
+        MB_LAUNCH("project_norm_rotate_store", project_norm_rotate_store_kernel<float>, dim3(tokens), dim3(threads), smem, stream, true,
+                  (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, q_bias, k_bias, v_bias, q_gain, k_gain, eps,
+                  positions, rotation, (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, value_dim, page_size);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("project_norm_rotate_store", project_norm_rotate_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream,
+                  true, (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_bias, k_bias,
+                  v_bias, q_gain, k_gain, eps, positions, rotation, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads,
+                  kv_heads, head_dim, value_dim, page_size);
+    else
+        return fail("project_norm_rotate_store: unknown dtype code %d", dtype);
+    return check_launch("project_norm_rotate_store");
 }

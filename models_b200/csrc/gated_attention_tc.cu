@@ -52,6 +52,7 @@ struct ScoreExtras {
     int sink;                 // != 0: the softmax's denominator has one more term of score 0
     const float* turn_cos;    // [positions][VD / 2] with turn_sin: the result's pairs are turned by minus the query's position
     const float* turn_sin;
+    int block;                // n > 0: a query sees only the keys of its own block of n positions (counted from 0); 0: every earlier key
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -147,6 +148,8 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
     const int pos0 = kv_len - q_len + t0;  // position of the tile's first token
     const int last_pos = pos0 + valid - 1;
     const int t_end = last_pos / kTile + 1;
+    // with blocks of visibility the first position any row of the tile sees is the lowest row's (the bound grows with the position)
+    const int t_begin = extras.block > 0 ? ((pos0 / extras.block) * extras.block) / kTile : 0;
     const float slope = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head + 1) / (float)heads) : 0.0f;
     const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
     constexpr float kLog2e = 1.4426950408889634f;
@@ -156,7 +159,7 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
 
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
-    load_stage(stage_base, k_pool, v_pool, table[0], kv_head, kv_heads);
+    load_stage(stage_base + (t_begin & 1) * kStageBytes, k_pool, v_pool, table[t_begin], kv_head, kv_heads);
     cp_async_commit();
     {
         constexpr int kPieces = KD / 8;
@@ -184,17 +187,20 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
         run_max[0] = run_max[1] = 0.0f;
         run_sum[0] = run_sum[1] = tid4 == 0 ? 1.0f : 0.0f;
     }
-    int row_pos[2];
+    int row_pos[2], row_low[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + group_id + 8 * r;
         row_pos[r] = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
+        row_low[r] = extras.block > 0 && row < valid ? (row_pos[r] / extras.block) * extras.block : 0;
     }
     const int warp_last = min(pos0 + warp * 16 + 15, last_pos);  // highest position among the warp's rows
     const int warp_first_pos = pos0 + warp * 16;                  // lowest
     const bool warp_has_rows = warp * 16 < valid;
+    const int warp_first_low = extras.block > 0 ? (warp_first_pos / extras.block) * extras.block : 0;  // lowest first-visible position
+    const int warp_low = extras.block > 0 ? (warp_last / extras.block) * extras.block : 0;  // highest first-visible position among the warp's rows
 
-    for (int t = 0; t < t_end; ++t) {
+    for (int t = t_begin; t < t_end; ++t) {
         const int stage = t & 1;
         if (t + 1 < t_end) {
             load_stage(stage_base + (stage ^ 1) * kStageBytes, k_pool, v_pool, table[t + 1], kv_head, kv_heads);
@@ -217,8 +223,8 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
                 *reinterpret_cast<uint4*>(rows + (first_stale + i / kPieces) * kValueRow + (i % kPieces) * 16) = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
         }
-        if (warp_has_rows && key_base <= warp_last) {
-            const bool full = key_base + kTile - 1 <= warp_first_pos && warp * 16 + 15 < valid;  // no mask needed
+        if (warp_has_rows && key_base <= warp_last && key_base + kTile > warp_first_low) {
+            const bool full = key_base + kTile - 1 <= warp_first_pos && warp * 16 + 15 < valid && key_base >= warp_low;  // no mask needed
             float s[kTile / 8][4];
 #pragma unroll
             for (int part = 0; part < kTile / 16; ++part) {
@@ -245,7 +251,7 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
                     float z = fmaf(s[nt][i], scale, bias) - slope * (float)(row_pos[r] - key);
                     // cap * tanh(z / cap) with tanh(x) = 1 - 2 / (1 + e^(2x))
                     if (cap > 0.0f) z = cap - __fdividef(2.0f * cap, 1.0f + fast_exp2(z * cap_exponent));
-                    if (!full && key > row_pos[r]) z = -CUDART_INF_F;
+                    if (!full && (key > row_pos[r] || key < row_low[r])) z = -CUDART_INF_F;
                     if (kSoftmax) {
                         part_max[r] = fmaxf(part_max[r], z);
                         s[nt][i] = z;
@@ -344,11 +350,11 @@ MB_EXPORT int mb_gated_attention_tc(const void* q, int q_stride, void* out, int 
                                     const float* head_bias, const void* gate, int gate_stride, int gate_kind, int sequences,
                                     int max_q_len, int heads, int kv_heads, int page_size, int softmax, float scale,
                                     float slope_exponent, const float* head_scale, float softcap, int sink, const float* turn_cos,
-                                    const float* turn_sin, cudaStream_t stream) {
+                                    const float* turn_sin, int block, cudaStream_t stream) {
     if (sequences <= 0 || max_q_len <= 0) return 0;
     if ((turn_cos == nullptr) != (turn_sin == nullptr)) return fail("gated_attention_tc: turning the result back needs both tables");
     if (softcap < 0.0f || (sink && !softmax)) return fail("gated_attention_tc: softcap %g, a sink without a softmax", softcap);
-    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin};
+    const ScoreExtras extras{head_scale, softcap, sink, turn_cos, turn_sin, block};
     if (page_size != kTile) return fail("gated_attention_tc: cache pages must hold %d positions, got %d", kTile, page_size);
     if (kv_heads <= 0 || heads % kv_heads) return fail("gated_attention_tc: %d heads are no multiple of %d kv heads", heads, kv_heads);
     if (sequences > 65535 || heads > 65535) return fail("gated_attention_tc: %d sequences or %d heads exceed the grid limit 65535", sequences, heads);

@@ -12,6 +12,14 @@
 // that are walked at the same time: each run first finds its own (A, B) with S_end = A S_start + B, the
 // starts follow from the sequence's stored state by composing the runs before, and a second walk writes
 // the results.  With one token per sequence (decoding) there is one run and one walk.
+//
+// Real-gated linear recurrent unit (gates read the convolved input u of the current token, through one small square matrix
+// per block of channels whose sums arrive as r_in and i_in):
+//   r_t = sigmoid(r_in_t + br)         i_t = sigmoid(i_in_t + bi)
+//   log a_t = rate * r_t   (rate = -c softplus(lambda) per channel, a number <= 0)        a_t = exp(log a_t)
+//   S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t                  (1 - a^2 is taken as -expm1(2 log a))
+//   y_t = out_scale * S_t * gelu_tanh(y_in_t + by)
+// r_in, i_in and u are float rows; y_in is a projection in the storage type.  The same runs and two walks as above.
 #include "common.cuh"
 
 MB_DEFINE_LAST_ERROR()
@@ -168,6 +176,92 @@ __global__ void __launch_bounds__(kBlockThreads) mingru_scan_kernel(const T* __r
     if (chunk == chunks - 1) *stored = s;  // runs after the last token are empty: this is the state after all of them
 }
 
+struct RglruCell {
+    float a, b;
+};
+
+// the gate sums of channel c lie block by block: [r of block 0 | i of block 0 | r of block 1 | ...], `per` channels a block
+__device__ __forceinline__ RglruCell rglru_cell(float r_sum, float i_sum, float u, float br, float bi, float rate) {
+    const float r = sigmoid(r_sum + br), i = sigmoid(i_sum + bi);
+    const float log_a = rate * r;
+    return RglruCell{expf(log_a), sqrtf(-expm1f(2.0f * log_a)) * i * u};
+}
+
+// grid (ceil(width / channels), sequences); block (channels, chunks) with channels * chunks <= 1024.
+template <typename T>
+__global__ void __launch_bounds__(kBlockThreads) rglru_scan_kernel(const float* __restrict__ gates, int gate_stride, int per,
+                                  const float* __restrict__ u, int u_stride, const T* __restrict__ y_in, int y_stride,
+                                  const float* __restrict__ r_bias, const float* __restrict__ i_bias, const float* __restrict__ y_bias,
+                                  const float* __restrict__ rate, float* __restrict__ state, size_t state_stride,
+                                  const int* __restrict__ slots, const int* __restrict__ cu_q, int width, T* __restrict__ out,
+                                  int out_stride, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    __shared__ float a_of[kBlockThreads];  // [run][channel of the block]
+    __shared__ float b_of[kBlockThreads];
+    const int seq = blockIdx.y;
+    const int first = cu_q[seq];
+    const int count = cu_q[seq + 1] - first;
+    if (count <= 0) return;  // the whole block leaves
+    const int channel = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = channel < width;
+    const int chunks = blockDim.y, chunk = threadIdx.y;
+    const int per_run = (count + chunks - 1) / chunks;
+    const int t0 = min(chunk * per_run, count), t1 = min(t0 + per_run, count);
+    const int c = live ? channel : 0;
+    const float br = r_bias[c], bi = i_bias[c], by = y_bias[c], channel_rate = rate[c];
+    const int r_at = (c / per) * 2 * per + c % per, i_at = r_at + per;
+    constexpr int kAhead = 8;  // loads do not depend on the recurrence: eight tokens' inputs are asked for before the first is used
+    if (chunks > 1) {
+        float a = 1.0f, b = 0.0f;
+        if (live) {
+            for (int t = t0; t < t1; t += kAhead) {
+                float rr[kAhead], ir[kAhead], ur[kAhead];
+#pragma unroll
+                for (int k = 0; k < kAhead; ++k) {
+                    const size_t token = first + min(t + k, t1 - 1);
+                    rr[k] = gates[token * gate_stride + r_at];
+                    ir[k] = gates[token * gate_stride + i_at];
+                    ur[k] = u[token * u_stride + c];
+                }
+#pragma unroll
+                for (int k = 0; k < kAhead; ++k) {
+                    if (t + k >= t1) break;
+                    const RglruCell cell = rglru_cell(rr[k], ir[k], ur[k], br, bi, channel_rate);
+                    a *= cell.a;
+                    b = cell.a * b + cell.b;
+                }
+            }
+        }
+        a_of[chunk * blockDim.x + threadIdx.x] = a;
+        b_of[chunk * blockDim.x + threadIdx.x] = b;
+        __syncthreads();
+    }
+    if (!live) return;
+    float* stored = state + (size_t)slots[seq] * state_stride + channel;
+    float s = *stored;
+    for (int before = 0; before < chunk; ++before) s = a_of[before * blockDim.x + threadIdx.x] * s + b_of[before * blockDim.x + threadIdx.x];
+    for (int t = t0; t < t1; t += kAhead) {
+        float rr[kAhead], ir[kAhead], ur[kAhead], yr[kAhead];
+#pragma unroll
+        for (int k = 0; k < kAhead; ++k) {
+            const size_t token = first + min(t + k, t1 - 1);
+            rr[k] = gates[token * gate_stride + r_at];
+            ir[k] = gates[token * gate_stride + i_at];
+            ur[k] = u[token * u_stride + c];
+            yr[k] = Num<T>::load(y_in + token * y_stride + c);
+        }
+#pragma unroll
+        for (int k = 0; k < kAhead; ++k) {
+            if (t + k >= t1) break;
+            const RglruCell cell = rglru_cell(rr[k], ir[k], ur[k], br, bi, channel_rate);
+            s = cell.a * s + cell.b;
+            Num<T>::store(out + (size_t)(first + t + k) * out_stride + c, out_scale * s * gate_activation(MB_ACT_GELU_TANH, yr[k] + by));
+        }
+    }
+    if (chunk == chunks - 1) *stored = s;  // runs after the last token are empty: this is the state after all of them
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -198,4 +292,31 @@ MB_EXPORT int mb_mingru_scan(const void* zin, const void* xin, const void* gin, 
     else
         return fail("mingru_scan: unknown dtype code %d", dtype);
     return check_launch("mingru_scan");
+}
+
+// gates: float [tokens, 2 * width] block by block (r sums then i sums of each block of `per` channels); u float [tokens, width];
+// y_in [tokens, width] in the storage type; biases and rate float [width]; state + slots[seq] * state_stride is [width] floats.
+MB_EXPORT int mb_rglru_scan(const float* gates, int gate_stride, int per, const float* u, int u_stride, const void* y_in, int y_stride,
+                            int dtype, const float* r_bias, const float* i_bias, const float* y_bias, const float* rate, float* state,
+                            size_t state_stride, const int* slots, const int* cu_q, int sequences, int max_q_len, int width, void* out,
+                            int out_stride, float out_scale, cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0 || width <= 0) return 0;
+    if (sequences > 65535) return fail("rglru_scan: %d sequences exceed the grid limit 65535", sequences);
+    if (per <= 0 || width % per) return fail("rglru_scan: %d channels are no whole blocks of %d", width, per);
+    int chunks = 1;
+    while (chunks < kMaxChunks && chunks * 16 < max_q_len) chunks *= 2;
+    int channels = chunks == 1 ? 128 : kBlockThreads / chunks;
+    if (channels > 32 && chunks > 1) channels = 32;
+    const dim3 grid((width + channels - 1) / channels, sequences), block(channels, chunks);
+    if (dtype == MB_F32)
+        MB_LAUNCH("rglru_scan", rglru_scan_kernel<float>, dim3(grid), dim3(block), 0, stream, true, gates, gate_stride, per, u, u_stride,
+                  (const float*)y_in, y_stride, r_bias, i_bias, y_bias, rate, state, state_stride, slots, cu_q, width, (float*)out,
+                  out_stride, out_scale);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH("rglru_scan", rglru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true, gates, gate_stride, per, u,
+                  u_stride, (const __nv_bfloat16*)y_in, y_stride, r_bias, i_bias, y_bias, rate, state, state_stride, slots, cu_q, width,
+                  (__nv_bfloat16*)out, out_stride, out_scale);
+    else
+        return fail("rglru_scan: unknown dtype code %d", dtype);
+    return check_launch("rglru_scan");
 }

@@ -136,7 +136,7 @@ struct GemmArgs {
     // reads (it is left out; its rows of the output are not written).  The table is written by a kernel before.
     const int* tile_group;    // null: a plain product
     int group_rows;           // rows of W per group (EPI_SWIGLU: gate rows; the up rows of the same group lie up_row_offset further)
-    float limit, slope;       // activation kClampedSwish: min(gate, limit) * sigmoid(slope * that) * (clamp(up, -limit, limit) + 1)
+    float limit, slope, up_offset;  // activation kClampedSwish: min(gate, limit) * sigmoid(slope * that) * (clamp(up, -limit, limit) + up_offset)
 };
 
 constexpr int kClampedSwish = 100;  // (beside the MB_ACT_* codes; only the grouped entry point sets it)
@@ -471,7 +471,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 for (int i = 0; i < 32; ++i) {
                                     if (args.activation == kClampedSwish) {
                                         const float g = fminf(v[i], args.limit), up = fminf(fmaxf(u[i], -args.limit), args.limit);
-                                        v[i] = g / (1.0f + expf(-args.slope * g)) * (up + 1.0f);
+                                        v[i] = g / (1.0f + expf(-args.slope * g)) * (up + args.up_offset);
                                     } else {
                                         v[i] = gate_activation(args.activation, v[i]) * u[i];
                                     }
@@ -849,7 +849,7 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
 //             rows; out bfloat16 [m, n] = clamped_swish(gate, up) with `limit` and `slope`.
 // gated == 0: group g's `n` rows at row g * n; out float32 [m, n].
 MB_EXPORT int mb_gemm_tcgen05_grouped(const void* a, int lda, const void* w, int ldw, int w_rows, void* out, int ld_out, int m, int n,
-                                      int k, int gated, int up_row_offset, const int* tile_group, float limit, float slope,
+                                      int k, int gated, int up_row_offset, const int* tile_group, float limit, float slope, float up_offset,
                                       int multiprocessors, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (tile_group == nullptr) return fail("gemm_tcgen05_grouped: the table of the tiles' groups is missing");
@@ -862,7 +862,7 @@ MB_EXPORT int mb_gemm_tcgen05_grouped(const void* a, int lda, const void* w, int
     if (int status = make_map(&map_w, w, w_rows, k, ldw)) return status;
     GemmArgs args{};
     args.m = m; args.n = n; args.k = k; args.up_row_offset = up_row_offset; args.activation = kClampedSwish; args.k_splits = 1;
-    args.out = out; args.ld_out = ld_out; args.tile_group = tile_group; args.group_rows = n; args.limit = limit; args.slope = slope;
+    args.out = out; args.ld_out = ld_out; args.tile_group = tile_group; args.group_rows = n; args.limit = limit; args.slope = slope; args.up_offset = up_offset;
     if (gated) return launch_tile<EPI_SWIGLU, 256, 1>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI_F32, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }

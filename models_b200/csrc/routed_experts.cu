@@ -2,7 +2,8 @@
 //
 //   router:   z = R x (float sums), the `top` largest (ties to the lower index), weights = softmax over the chosen z
 //   sort:     the (token, choice) entries grouped by expert, in token order, cut into tiles of 64 rows
-//   expert e: g = min(Wg_e x, limit), u = clamp(Wu_e x, -limit, limit), y = Wd_e (g * sigmoid(slope * g) * (u + 1))
+//   expert e: g = min(Wg_e x, limit), u = clamp(Wu_e x, -limit, limit), y = Wd_e (g * sigmoid(slope * g) * (u + up_offset))
+//             (limit +inf, slope 1, up_offset 0: the plain gated form silu(g) * u)
 //   combine:  out[token] = sum_choice weight * y[token, choice] (+ sigmoid(score[token]) * shared[token])
 //
 // The two expert products are grouped products: a block owns one tile of one expert's rows and 64 output columns, reads
@@ -24,11 +25,23 @@ constexpr int kMaxTop = 32;
 
 __device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
-__device__ __forceinline__ float clamped_swish(float g, float u, float limit, float slope) {
+__device__ __forceinline__ float clamped_swish(float g, float u, float limit, float slope, float up_offset) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g * sigmoid(slope * g) * (u + 1.0f);
+    return g * sigmoid(slope * g) * (u + up_offset);
 }
+
+// How a router turns logits into choices and weights.  scored == 0: the `top` largest logits, weights = softmax over the chosen
+// logits.  scored != 0: scores s = softmax over ALL logits; the choice runs on s + correction (a float per expert, or null);
+// the experts form `groups` equal groups of neighbours, a group counts by its largest choice score, and only experts of the
+// `keep` best groups can be chosen (ties to the lower index everywhere); weights = weight_scale * s of the chosen, not
+// renormalised.
+struct RouterRule {
+    int scored;
+    const float* correction;
+    int groups, keep;
+    float weight_scale;
+};
 
 // grid (ceil(tokens / kTokens)); block 256.  shared per token of the block: width floats (its row), experts floats (its logits).
 // kVector: width a multiple of 8 and rows on 16 (bfloat16) or 32 (float) bytes: a lane reads 8 elements of a router row with
@@ -37,12 +50,13 @@ __device__ __forceinline__ float clamped_swish(float g, float u, float limit, fl
 template <typename T, bool kVector, int kTokens>
 __global__ void __launch_bounds__(256)
 router_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int* __restrict__ chosen,
-                   float* __restrict__ weights, int tokens, int width, int experts, int top) {
+                   float* __restrict__ weights, int tokens, int width, int experts, int top, RouterRule rule) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float router_shared[];
     float* rows = router_shared;                       // [kTokens][width]
     float* all_logits = router_shared + kTokens * width;  // [kTokens][experts]
+    float* all_scores = all_logits + kTokens * experts;    // [kTokens][experts], a scored rule's softmax over all experts
     __shared__ float all_picked[kTokens][kMaxTop];
     const int token0 = blockIdx.x * kTokens, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int here = min(kTokens, tokens - token0);
@@ -103,6 +117,46 @@ router_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ 
     const int token = token0 + warp;
     float* logits = all_logits + warp * experts;
     float* picked = all_picked[warp];
+    if (rule.scored) {
+        // scores over all experts, kept in `all_scores` for the weights; logits[e] becomes the choice score (-inf outside the
+        // kept groups), on which the rounds of arg-max below run
+        float top_logit = -CUDART_INF_F;
+        for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, logits[e]);
+        top_logit = warp_max(top_logit);
+        float sum = 0.0f;
+        for (int e = lane; e < experts; e += 32) sum += expf(logits[e] - top_logit);
+        sum = warp_sum(sum);
+        float* scores = all_scores + warp * experts;
+        for (int e = lane; e < experts; e += 32) {
+            const float score = expf(logits[e] - top_logit) / sum;
+            scores[e] = score;
+            logits[e] = score + (rule.correction != nullptr ? rule.correction[e] : 0.0f);
+        }
+        __syncwarp();
+        if (rule.groups > 1 && rule.keep < rule.groups) {
+            // lane g finds group g's best choice score (groups <= 32); `keep` rounds pick the best groups; the others close
+            const int per = experts / rule.groups;
+            float group_best = -CUDART_INF_F;
+            if (lane < rule.groups)
+                for (int e = lane * per; e < (lane + 1) * per; ++e) group_best = fmaxf(group_best, logits[e]);
+            bool kept = false;
+            for (int round = 0; round < rule.keep; ++round) {
+                float best = (lane < rule.groups && !kept) ? group_best : -CUDART_INF_F;
+                int index = (lane < rule.groups && !kept) ? lane : 0x7fffffff;
+#pragma unroll
+                for (int offset = 16; offset > 0; offset >>= 1) {
+                    const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+                    const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+                    if (other > best || (other == best && other_index < index)) best = other, index = other_index;
+                }
+                if (lane == index) kept = true;
+            }
+            const unsigned open = __ballot_sync(0xffffffffu, kept);
+            for (int e = lane; e < experts; e += 32)
+                if (!((open >> (e / per)) & 1u)) logits[e] = -CUDART_INF_F;
+            __syncwarp();
+        }
+    }
     for (int s = 0; s < top; ++s) {
         // the largest logit that is not taken yet; ties go to the lower index (a taken expert's logit is -inf)
         float best = -CUDART_INF_F;
@@ -126,6 +180,11 @@ router_topk_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ 
         __syncwarp();
     }
     __syncwarp();
+    if (rule.scored) {
+        const float* scores = all_scores + warp * experts;
+        if (lane < top) weights[(size_t)token * top + lane] = rule.weight_scale * scores[chosen[(size_t)token * top + lane]];
+        return;
+    }
     if (lane == 0) {
         const float top_logit = picked[0];  // the largest: the first one picked
         float sum = 0.0f;
@@ -355,7 +414,7 @@ __global__ void __launch_bounds__(256)
 expert_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0, const T* __restrict__ w1,
                       T* __restrict__ mid, float* __restrict__ slot_out, int out_stride, const int* __restrict__ sorted,
                       const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row,
-                      int top, int N, int K, float limit, float slope) {
+                      int top, int N, int K, float limit, float slope, float up_offset) {
     grid_launch_dependents();
     grid_dependency_wait();
     constexpr int kStep = 16;
@@ -419,7 +478,7 @@ expert_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (kFirst)
-                Num<T>::store(mid + (size_t)(row0 + r) * out_stride + n, clamped_swish(acc[0][i][j], acc[kFirst ? 1 : 0][i][j], limit, slope));
+                Num<T>::store(mid + (size_t)(row0 + r) * out_stride + n, clamped_swish(acc[0][i][j], acc[kFirst ? 1 : 0][i][j], limit, slope, up_offset));
             else
                 slot_out[(size_t)sorted[row0 + r] * out_stride + n] = acc[0][i][j];
         }
@@ -436,7 +495,7 @@ template <typename T, bool kFirst, bool kVector>
 __global__ void __launch_bounds__(256)
 expert_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0, const T* __restrict__ w1, T* __restrict__ mid,
                    float* __restrict__ slot_out, int out_stride, const int* __restrict__ chosen, int top, int experts, int N, int K,
-                   float limit, float slope) {
+                   float limit, float slope, float up_offset) {
     grid_launch_dependents();
     grid_dependency_wait();
     constexpr int kCols = 4;
@@ -504,7 +563,7 @@ expert_rows_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
         const int n = n0 + j;
         if (n >= N) break;
         if (kFirst)
-            Num<T>::store(mid + (size_t)entry * out_stride + n, clamped_swish(acc[0][j], acc[kSets - 1][j], limit, slope));
+            Num<T>::store(mid + (size_t)entry * out_stride + n, clamped_swish(acc[0][j], acc[kSets - 1][j], limit, slope, up_offset));
         else
             slot_out[(size_t)entry * out_stride + n] = acc[0][j];
     }
@@ -546,7 +605,7 @@ __global__ void __launch_bounds__(128)
 expert_product_tc_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                          bf16* __restrict__ mid, float* __restrict__ slot_out, int out_stride, const int* __restrict__ sorted,
                          const int* __restrict__ offsets, const int* __restrict__ tile_expert, const int* __restrict__ tile_row,
-                         int top, int N, int K, float limit, float slope) {
+                         int top, int N, int K, float limit, float slope, float up_offset) {
     grid_launch_dependents();
     grid_dependency_wait();
     constexpr int kSets = kFirst ? 2 : 1;
@@ -636,7 +695,7 @@ expert_product_tc_kernel(const bf16* __restrict__ a, int a_stride, const bf16* _
                 if (n >= N) continue;
                 const float v0 = acc[0][nt][2 * half + c];
                 if (kFirst)
-                    mid[out_row * out_stride + n] = __float2bfloat16_rn(clamped_swish(v0, acc[kSets - 1][nt][2 * half + c], limit, slope));
+                    mid[out_row * out_stride + n] = __float2bfloat16_rn(clamped_swish(v0, acc[kSets - 1][nt][2 * half + c], limit, slope, up_offset));
                 else
                     slot_out[out_row * out_stride + n] = v0;
             }
@@ -649,7 +708,7 @@ expert_product_tc_kernel(const bf16* __restrict__ a, int a_stride, const bf16* _
 // out[t][c] = clamped_swish(gate[t][c], up[t][c]); grid (ceil(rows * cols / 256)); block 256.
 template <typename T>
 __global__ void clamped_swish_kernel(const T* __restrict__ gate, const T* __restrict__ up, int in_stride, T* __restrict__ out,
-                                     int out_stride, size_t total, int cols, float limit, float slope) {
+                                     int out_stride, size_t total, int cols, float limit, float slope, float up_offset) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -657,7 +716,7 @@ __global__ void clamped_swish_kernel(const T* __restrict__ gate, const T* __rest
     const size_t t = i / cols;
     const int c = (int)(i % cols);
     Num<T>::store(out + t * out_stride + c,
-                  clamped_swish(Num<T>::load(gate + t * in_stride + c), Num<T>::load(up + t * in_stride + c), limit, slope));
+                  clamped_swish(Num<T>::load(gate + t * in_stride + c), Num<T>::load(up + t * in_stride + c), limit, slope, up_offset));
 }
 
 // out[t][c] = sum_s weights[t][s] * slot_out[t * top + s][c] (+ sigmoid(score[t]) * shared[t][c]); float out.
@@ -665,7 +724,8 @@ __global__ void clamped_swish_kernel(const T* __restrict__ gate, const T* __rest
 template <typename T>
 __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const float* __restrict__ weights,
                                       const float* __restrict__ shared, const T* __restrict__ score, int score_stride,
-                                      float* __restrict__ out, size_t total, int width, int top, const int* __restrict__ position) {
+                                      float* __restrict__ out, size_t total, int width, int top, const int* __restrict__ position,
+                                      const int* __restrict__ chosen, int experts, const T* __restrict__ rows, int rows_stride) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -674,10 +734,14 @@ __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const 
     const int c = (int)(i % width);
     float sum = 0.0f;
     for (int s = 0; s < top; ++s) {
+        if (chosen != nullptr && chosen[t * top + s] >= experts) {  // an identity expert: its result is the token's own row
+            sum = fmaf(weights[t * top + s], Num<T>::load(rows + t * rows_stride + c), sum);
+            continue;
+        }
         const size_t row = position != nullptr ? (size_t)position[t * top + s] : t * top + s;  // where the entry's result lies
         sum = fmaf(weights[t * top + s], slot_out[row * width + c], sum);
     }
-    if (shared != nullptr) sum = fmaf(sigmoid(Num<T>::load(score + t * score_stride)), shared[i], sum);
+    if (shared != nullptr) sum = fmaf(score != nullptr ? sigmoid(Num<T>::load(score + t * score_stride)) : 1.0f, shared[i], sum);
     out[i] = sum;
 }
 
@@ -685,7 +749,8 @@ __global__ void expert_combine_kernel(const float* __restrict__ slot_out, const 
 template <typename T>
 __global__ void expert_combine_vec4_kernel(const float* __restrict__ slot_out, const float* __restrict__ weights,
                                            const float* __restrict__ shared, const T* __restrict__ score, int score_stride,
-                                           float* __restrict__ out, size_t total4, int width, int top, const int* __restrict__ position) {
+                                           float* __restrict__ out, size_t total4, int width, int top, const int* __restrict__ position,
+                                           const int* __restrict__ chosen, int experts, const T* __restrict__ rows, int rows_stride) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -695,13 +760,19 @@ __global__ void expert_combine_vec4_kernel(const float* __restrict__ slot_out, c
     const int c = (int)(i % quads) * 4;
     float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int s = 0; s < top; ++s) {
-        const size_t row = position != nullptr ? (size_t)position[t * top + s] : t * top + s;
         const float w = weights[t * top + s];
+        if (chosen != nullptr && chosen[t * top + s] >= experts) {  // an identity expert: its result is the token's own row
+            const T* own = rows + t * rows_stride + c;
+            sum.x = fmaf(w, Num<T>::load(own), sum.x); sum.y = fmaf(w, Num<T>::load(own + 1), sum.y);
+            sum.z = fmaf(w, Num<T>::load(own + 2), sum.z); sum.w = fmaf(w, Num<T>::load(own + 3), sum.w);
+            continue;
+        }
+        const size_t row = position != nullptr ? (size_t)position[t * top + s] : t * top + s;
         const float4 v = *reinterpret_cast<const float4*>(slot_out + row * width + c);
         sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
     }
     if (shared != nullptr) {
-        const float g = sigmoid(Num<T>::load(score + t * score_stride));
+        const float g = score != nullptr ? sigmoid(Num<T>::load(score + t * score_stride)) : 1.0f;
         const float4 v = *reinterpret_cast<const float4*>(shared + t * width + c);
         sum.x = fmaf(g, v.x, sum.x); sum.y = fmaf(g, v.y, sum.y); sum.z = fmaf(g, v.z, sum.z); sum.w = fmaf(g, v.w, sum.w);
     }
@@ -716,11 +787,16 @@ MB_EXPORT int mb_route_tile_rows() { return kTileRows; }
 MB_EXPORT int mb_route_max_top() { return kMaxTop; }
 
 MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, int dtype, int* chosen, float* weights, int tokens,
-                             int width, int experts, int top, cudaStream_t stream) {
+                             int width, int experts, int top, int scored, const float* correction, int groups, int keep,
+                             float weight_scale, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > kMaxTop)
         return fail("router_topk: width %d, %d experts, top %d (at most %d and the number of experts)", width, experts, top, kMaxTop);
-    const size_t one = ((size_t)width + experts) * sizeof(float);
+    if (scored && (groups < 1 || groups > 32 || experts % groups || keep < 1 || keep > groups))
+        return fail("router_topk: %d groups (at most 32, dividing the %d experts) of which %d are kept", groups, experts, keep);
+    if (scored && top > (experts / groups) * keep) return fail("router_topk: top %d exceeds the %d experts of the kept groups", top, (experts / groups) * keep);
+    const RouterRule rule{scored, correction, groups, keep, weight_scale};
+    const size_t one = ((size_t)width + 2 * (size_t)experts) * sizeof(float);
     if (one > 200 * 1024) return fail("router_topk: a row of %d and %d logits exceed a block's shared memory", width, experts);
     const size_t unit = dtype == MB_F32 ? 32 : 16, element = dtype == MB_F32 ? 4 : 2;
     const bool vector = width % 8 == 0 && ((size_t)x_stride * element) % unit == 0 && !((uintptr_t)x % unit) && !((uintptr_t)router % unit);
@@ -735,7 +811,7 @@ MB_EXPORT int mb_router_topk(const void* x, int x_stride, const void* router, in
         if (smem > 48 * 1024)                                                                                                         \
             cudaFuncSetAttribute(router_topk_kernel<T, VECTOR, TOKENS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         MB_LAUNCH("router_topk", (router_topk_kernel<T, VECTOR, TOKENS>), dim3((tokens + TOKENS - 1) / TOKENS), dim3(256), smem, stream, \
-                  true, (const T*)x, x_stride, (const T*)router, chosen, weights, tokens, width, experts, top);                       \
+                  true, (const T*)x, x_stride, (const T*)router, chosen, weights, tokens, width, experts, top, rule);                       \
     } while (0)
     if (dtype == MB_F32) {
         if (many) MB_ROUTER(float, true, kMany); else if (together) MB_ROUTER(float, true, kTogether); else if (vector) MB_ROUTER(float, true, 1); else MB_ROUTER(float, false, 1);
@@ -804,7 +880,7 @@ MB_EXPORT int mb_gather_rows(const void* x, int x_stride, const int* sorted, con
 // first == 0: a = mid [entries][K], w0 = down [experts][N][K], slot_out [entries][N] (float) written by entry id.
 MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, const void* w1, void* mid, float* slot_out, int out_stride,
                                 int dtype, const int* sorted, const int* offsets, const int* tile_expert, const int* tile_row,
-                                int max_tiles, int top, int N, int K, float limit, float slope, int first, int tensor_cores,
+                                int max_tiles, int top, int N, int K, float limit, float slope, float up_offset, int first, int tensor_cores,
                                 cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0 || top <= 0) return fail("expert_product: N %d, K %d, top %d", N, K, top);
@@ -822,7 +898,7 @@ MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, con
                 configured = true;
             }
             MB_LAUNCH("expert_product_tc", expert_product_tc_kernel<true>, grid, dim3(128), smem, stream, true, (const bf16*)a, a_stride,
-                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope);
+                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope, up_offset);
         } else {
             const size_t smem = 2 * 2 * (size_t)kTileRows * kRowBytes;
             static bool configured = false;
@@ -832,13 +908,13 @@ MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, con
                 configured = true;
             }
             MB_LAUNCH("expert_product_tc", expert_product_tc_kernel<false>, grid, dim3(128), smem, stream, true, (const bf16*)a, a_stride,
-                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope);
+                      (const bf16*)w0, (const bf16*)w1, (bf16*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope, up_offset);
         }
         return 0;
     }
 #define MB_PRODUCT(T, FIRST)                                                                                                        \
     MB_LAUNCH("expert_product", (expert_product_kernel<T, FIRST>), grid, dim3(256), 0, stream, true, (const T*)a, a_stride, (const T*)w0, \
-              (const T*)w1, (T*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope)
+              (const T*)w1, (T*)mid, slot_out, out_stride, sorted, offsets, tile_expert, tile_row, top, N, K, limit, slope, up_offset)
     if (dtype == MB_F32) {
         if (first) MB_PRODUCT(float, true); else MB_PRODUCT(float, false);
     } else if (dtype == MB_BF16) {
@@ -852,7 +928,7 @@ MB_EXPORT int mb_expert_product(const void* a, int a_stride, const void* w0, con
 
 // The products for few entries (see expert_rows_kernel); rows of mid and slot_out in entry order (token * top + choice).
 MB_EXPORT int mb_expert_rows(const void* a, int a_stride, const void* w0, const void* w1, void* mid, float* slot_out, int out_stride,
-                             int dtype, const int* chosen, int entries, int top, int experts, int N, int K, float limit, float slope,
+                             int dtype, const int* chosen, int entries, int top, int experts, int N, int K, float limit, float slope, float up_offset,
                              int first, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (N <= 0 || K <= 0 || top <= 0 || experts <= 0) return fail("expert_rows: N %d, K %d, top %d, %d experts", N, K, top, experts);
@@ -868,7 +944,7 @@ MB_EXPORT int mb_expert_rows(const void* a, int a_stride, const void* w0, const 
     do {                                                                                                                             \
         if (smem > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<T, FIRST, VECTOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         MB_LAUNCH("expert_rows", (expert_rows_kernel<T, FIRST, VECTOR>), grid, dim3(256), smem, stream, true, (const T*)a, a_stride,  \
-                  (const T*)w0, (const T*)w1, (T*)mid, slot_out, out_stride, chosen, top, experts, N, K, limit, slope);               \
+                  (const T*)w0, (const T*)w1, (T*)mid, slot_out, out_stride, chosen, top, experts, N, K, limit, slope, up_offset);               \
     } while (0)
 #define MB_ROWS_OF(T)                                                              \
     do {                                                                           \
@@ -886,26 +962,29 @@ MB_EXPORT int mb_expert_rows(const void* a, int a_stride, const void* w0, const 
 }
 
 MB_EXPORT int mb_clamped_swish(const void* gate, const void* up, int in_stride, void* out, int out_stride, int dtype, int rows, int cols,
-                               float limit, float slope, cudaStream_t stream) {
+                               float limit, float slope, float up_offset, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     const size_t total = (size_t)rows * cols;
     const dim3 grid((unsigned)((total + 255) / 256));
     if (dtype == MB_F32)
         MB_LAUNCH("clamped_swish", clamped_swish_kernel<float>, grid, dim3(256), 0, stream, true, (const float*)gate, (const float*)up, in_stride,
-                  (float*)out, out_stride, total, cols, limit, slope);
+                  (float*)out, out_stride, total, cols, limit, slope, up_offset);
     else if (dtype == MB_BF16)
         MB_LAUNCH("clamped_swish", clamped_swish_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, (const __nv_bfloat16*)gate,
-                  (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, out_stride, total, cols, limit, slope);
+                  (const __nv_bfloat16*)up, in_stride, (__nv_bfloat16*)out, out_stride, total, cols, limit, slope, up_offset);
     else
         return fail("clamped_swish: unknown dtype code %d", dtype);
     return 0;
 }
 
-// shared may be null (no shared expert); score is one number per token of the storage type `dtype` (stride in elements).
+// shared may be null (no shared expert); score (or null: the shared expert is added as it is) is one number per token of the
+// storage type `dtype` (stride in elements).  With `chosen` [tokens * top], an entry whose expert is >= `experts` is an identity
+// expert: its result is the token's own row of `rows` (storage type, stride in elements).
 MB_EXPORT int mb_expert_combine(const float* slot_out, const float* weights, const float* shared, const void* score, int score_stride,
-                                int dtype, float* out, int tokens, int width, int top, const int* position, cudaStream_t stream) {
+                                int dtype, float* out, int tokens, int width, int top, const int* position, const int* chosen,
+                                int experts, const void* rows, int rows_stride, cudaStream_t stream) {
     if (tokens <= 0 || width <= 0) return 0;
-    if (shared != nullptr && score == nullptr) return fail("expert_combine: a shared expert needs its gate scores");
+    if (chosen != nullptr && rows == nullptr) return fail("expert_combine: identity experts need the tokens' rows");
     const size_t total = (size_t)tokens * width;
     if (dtype != MB_F32 && dtype != MB_BF16) return fail("expert_combine: unknown dtype code %d", dtype);
     if (width % 4 == 0 && !((uintptr_t)slot_out & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared & 15)) {
@@ -913,19 +992,19 @@ MB_EXPORT int mb_expert_combine(const float* slot_out, const float* weights, con
         const dim3 grid4((unsigned)((total4 + 255) / 256));
         if (dtype == MB_F32)
             MB_LAUNCH("expert_combine", expert_combine_vec4_kernel<float>, grid4, dim3(256), 0, stream, true, slot_out, weights, shared,
-                      (const float*)score, score_stride, out, total4, width, top, position);
+                      (const float*)score, score_stride, out, total4, width, top, position, chosen, experts, (const float*)rows, rows_stride);
         else
             MB_LAUNCH("expert_combine", expert_combine_vec4_kernel<__nv_bfloat16>, grid4, dim3(256), 0, stream, true, slot_out, weights, shared,
-                      (const __nv_bfloat16*)score, score_stride, out, total4, width, top, position);
+                      (const __nv_bfloat16*)score, score_stride, out, total4, width, top, position, chosen, experts, (const __nv_bfloat16*)rows, rows_stride);
         return 0;
     }
     const dim3 grid((unsigned)((total + 255) / 256));
     if (dtype == MB_F32)
         MB_LAUNCH("expert_combine", expert_combine_kernel<float>, grid, dim3(256), 0, stream, true, slot_out, weights, shared, (const float*)score,
-                  score_stride, out, total, width, top, position);
+                  score_stride, out, total, width, top, position, chosen, experts, (const float*)rows, rows_stride);
     else if (dtype == MB_BF16)
         MB_LAUNCH("expert_combine", expert_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, true, slot_out, weights, shared,
-                  (const __nv_bfloat16*)score, score_stride, out, total, width, top, position);
+                  (const __nv_bfloat16*)score, score_stride, out, total, width, top, position, chosen, experts, (const __nv_bfloat16*)rows, rows_stride);
     else
         return fail("expert_combine: unknown dtype code %d", dtype);
     return 0;

@@ -12,6 +12,7 @@ LIBRARIES = [
     ("mb_sampling", ["sampling.cu"], {}),
     ("mb_talking_attention", ["talking_attention.cu"], {}),
     ("mb_gated_recurrence", ["gated_recurrence.cu"], {}),
+    ("mb_gated_delta", ["gated_delta.cu"], {}),
     ("mb_gated_attention", ["gated_attention.cu"], {}),
     ("mb_retention", ["retention.cu"], {}),
     ("mb_hyper_streams", ["hyper_streams.cu"], {}),

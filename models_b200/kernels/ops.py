@@ -269,16 +269,16 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out_dtype: torch.dtype,
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Layer norm with gain and bias of the float residual rows x [T, width] (of the rows picked by `rows`,
+    """Layer norm with gain and bias (None: no bias) of the float residual rows x [T, width] (of the rows picked by `rows`,
     if given): mean, variance and the result in float, stored as `out_dtype`."""
     _cuda(x, weight, bias, rows)
     if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
         raise KernelError("the residual stream must be a contiguous float32 [rows, width] tensor")
     width = x.shape[1]
     for name, t in (("weight", weight), ("bias", bias)):
-        if t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous():
+        if t is not None and (t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous()):
             raise KernelError(f"layer norm {name} must be contiguous float32 of {width} elements")
     _int32(rows, "rows")
     out_rows = rows.numel() if rows is not None else x.shape[0]
@@ -286,6 +286,58 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: fl
     lib = elementwise()
     _run(lib, lib.mb_layernorm(_p(x), _p(weight), _p(bias), _p(out), _code(out_dtype), _p(rows), out_rows, width,
                                ctypes.c_float(eps), _stream()))
+    return out
+
+
+def outnorm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, eps: float,
+                b: Optional[torch.Tensor] = None, gain_a: Optional[torch.Tensor] = None, gain_b: Optional[torch.Tensor] = None,
+                copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += scale * LN(y) in place on the float32 stream x [T, width], where LN(y) = (y - mean) / sqrt(var + eps) * weight
+    (no bias) and y is the sublayer's float32 result `a`, or -- given a second result `b` -- the mean of the two after an RMS
+    norm each, y = 1/2 (a / rms(a) * gain_a + b / rms(b) * gain_b).  With `copy_dtype` the new rows of x are also returned
+    in that type (what the next sublayer's products read)."""
+    _cuda(x, a, b, gain_a, gain_b, weight, scale)
+    width = x.shape[1]
+    for name, t in (("x", x), ("a", a), ("b", b)):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != tuple(x.shape) or not t.is_contiguous()):
+            raise KernelError(f"outnorm_add: {name} must be contiguous float32 {tuple(x.shape)}")
+    for name, t in (("weight", weight), ("scale", scale), ("gain_a", gain_a), ("gain_b", gain_b)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous()):
+            raise KernelError(f"outnorm_add: {name} must be contiguous float32 of {width} elements")
+    if b is not None and (gain_a is None or gain_b is None):
+        raise KernelError("outnorm_add: two results need two gains")
+    copy = torch.empty_like(x, dtype=copy_dtype) if copy_dtype is not None else None
+    lib = elementwise()
+    _run(lib, lib.mb_outnorm_add(_p(x), _p(a), _p(b), _p(gain_a), _p(gain_b), _p(weight), _p(scale), _p(copy),
+                                 _code(copy_dtype) if copy_dtype is not None else _F32, x.shape[0], width, ctypes.c_float(eps), _stream()))
+    return copy
+
+
+def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, eps: float) -> torch.Tensor:
+    """1/2 (a / rms(a) * gain_a + b / rms(b) * gain_b) row by row, rms(v) = sqrt(mean(v^2) + eps); float32 [T, width]."""
+    _cuda(a, b, gain_a, gain_b)
+    width = a.shape[1]
+    for name, t in (("a", a), ("b", b)):
+        if t.dtype != torch.float32 or tuple(t.shape) != tuple(a.shape) or not t.is_contiguous():
+            raise KernelError(f"pair_norm_mean: {name} must be contiguous float32 {tuple(a.shape)}")
+    for name, t in (("gain_a", gain_a), ("gain_b", gain_b)):
+        if t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous():
+            raise KernelError(f"pair_norm_mean: {name} must be contiguous float32 of {width} elements")
+    out = torch.empty_like(a)
+    lib = elementwise()
+    _run(lib, lib.mb_outnorm_add(_p(out), _p(a), _p(b), _p(gain_a), _p(gain_b), None, None, None, _F32, a.shape[0], width,
+                                 ctypes.c_float(eps), _stream()))
+    return out
+
+
+def store_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 rows x stored as `dtype` (what a matrix product of that type reads)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("store_rows: the rows must be contiguous float32")
+    out = torch.empty_like(x, dtype=dtype)
+    lib = elementwise()
+    _run(lib, lib.mb_store_rows(_p(x), _p(out), _code(dtype), ctypes.c_size_t(x.numel()), _stream()))
     return out
 
 
@@ -585,6 +637,46 @@ def rotate_norm_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positio
                                        head_dim, value_dim, page_size, _stream()))
 
 
+def project_norm_rotate_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_bias: Optional[torch.Tensor],
+                              k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor], q_gain: Optional[torch.Tensor],
+                              k_gain: Optional[torch.Tensor], eps: float, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                              sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, k_pool: torch.Tensor,
+                              v_pool: torch.Tensor, slot_mapping: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                              value_dim: int) -> None:
+    """Projections normalised as a whole: q <- (q + q_bias) / rms(q + q_bias) * q_gain over ALL heads of the row at once
+    (rms(x) = sqrt(mean(x^2) + eps); a gain of None: no norm), the same for k; then every head's first `rotary_dim` coordinates
+    are rotated by the token's position (float32 tables [positions, rotary_dim / 2]; pairs (i, i + rotary_dim / 2), or
+    (2i, 2i + 1) when `interleaved`); q is rewritten in place, k goes into the key pool at `slot_mapping`, v + v_bias into the
+    value pool.  q, k, v may be column slices of one tensor; biases and gains are float32."""
+    _cuda(q, k, v, q_bias, k_bias, v_bias, q_gain, k_gain, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    tokens = k.shape[0]
+    for name, t, width, extra in (("q", q, heads * head_dim, (q_bias, q_gain)), ("k", k, kv_heads * head_dim, (k_bias, k_gain)),
+                                  ("v", v, kv_heads * value_dim, (v_bias,))):
+        _columns(t, name)
+        if t.shape[1] != width or t.shape[0] != tokens or t.dtype != k.dtype:
+            raise KernelError(f"project_norm_rotate_store: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {k.dtype} is needed")
+        for vector in extra:
+            if vector is not None and (vector.dtype != torch.float32 or vector.numel() != width or not vector.is_contiguous()):
+                raise KernelError(f"project_norm_rotate_store: the bias and gain of {name} must be contiguous float32 of {width} elements")
+    if rotary_dim:
+        for table in (cos, sin):
+            if table is None or table.dtype != torch.float32 or table.dim() != 2 or table.shape[1] * 2 != rotary_dim or not table.is_contiguous():
+                raise KernelError(f"project_norm_rotate_store: rotary_dim {rotary_dim} needs contiguous float32 tables [positions, {rotary_dim // 2}]")
+    page_size = k_pool.shape[2]
+    if tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or not k_pool.is_contiguous() or k_pool.dtype != k.dtype:
+        raise KernelError(f"project_norm_rotate_store: the key pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}] of {k.dtype}")
+    if tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim) or not v_pool.is_contiguous() or v_pool.dtype != k.dtype:
+        raise KernelError(f"project_norm_rotate_store: the value pool must be contiguous [pages, {kv_heads}, page_size, {value_dim}] of {k.dtype}")
+    lib = gated_attention_library()
+    _run(lib, lib.mb_project_norm_rotate_store(
+        _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _code(k.dtype), _p(q_bias), _p(k_bias), _p(v_bias), _p(q_gain),
+        _p(k_gain), ctypes.c_float(eps), _p(positions), _p(cos) if rotary_dim else None, _p(sin) if rotary_dim else None,
+        int(rotary_dim), 1 if interleaved else 0, _p(k_pool), _p(v_pool), _p(slot_mapping), tokens, heads, kv_heads, head_dim,
+        value_dim, page_size, _stream()))
+
+
 GATE_KINDS = {None: 0, "head": 1, "element": 2}
 
 
@@ -628,7 +720,7 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
                     head_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                     gate_kind: Optional[str] = None, kernel: Optional[str] = None, head_scale: Optional[torch.Tensor] = None,
                     softcap: float = 0.0, sink: bool = False, turn_cos: Optional[torch.Tensor] = None,
-                    turn_sin: Optional[torch.Tensor] = None) -> None:
+                    turn_sin: Optional[torch.Tensor] = None, block: int = 0) -> None:
     """Causal attention over the paged cache with `weights` "softmax" or "sigmoid" (independent sigmoids of the scores,
     not normalised over keys); score = scale * q.k - 2^(-slope_exponent (h + 1) / heads) * (i - j) + head_bias[h]
     (slope_exponent 0: no distance term; head_bias None: 0).  `v_pool` None: the values are the first `value_dim`
@@ -638,6 +730,8 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
     else, becomes c * tanh(score / c); `sink`: the softmax's denominator has one more term of score 0 without a value;
     `turn_cos`, `turn_sin` (float32 [positions, value_dim / 2]): the values were stored rotated by their own positions
     (pairs 2m, 2m + 1), and every head's sum is turned back by the query's position before any gate.
+    `block` n > 0: query i sees key j <= i only if floor(i / n) = floor(j / n), blocks of n positions counted from the
+    sequence's position 0.
     `kernel`: None picks the decode form for steps of one token per sequence (the keys cut into runs with a block each;
     the grid follows the page table's width, not the lengths, so that a captured step stays valid), the tensor-core form
     where it applies (bfloat16 steps of many tokens), else the form with a warp per (token, head); "decode", "tc" or
@@ -684,7 +778,9 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
                 raise KernelError(f"gated_attention: the tables that turn the result back must be contiguous float32 [positions, {value_dim // 2}]")
     if sink and weights != "softmax":
         raise KernelError("gated_attention: a sink belongs to softmax weights")
-    extras = (_p(head_scale), ctypes.c_float(softcap), 1 if sink else 0, _p(turn_cos), _p(turn_sin))
+    if block < 0:
+        raise KernelError(f"gated_attention: a block of {block} positions")
+    extras = (_p(head_scale), ctypes.c_float(softcap), 1 if sink else 0, _p(turn_cos), _p(turn_sin), int(block))
     softmax = 1 if weights == "softmax" else 0
     sequences = kv_lens.numel()
     gate_stride = gate.stride(0) if gate is not None else 0
@@ -866,6 +962,123 @@ def mingru_scan(zin: torch.Tensor, xin: torch.Tensor, gin: torch.Tensor, z_bias:
     _run(lib, lib.mb_mingru_scan(_p(zin), _p(xin), _p(gin), zin.stride(0), _code(zin.dtype), _p(z_bias), _p(x_bias), _p(state),
                                  _p(slots), _p(cu_q), cu_q.numel() - 1, max_q_len, width, _p(out), out.stride(0),
                                  ctypes.c_float(out_scale), _stream()))
+
+
+def gated_delta_library():
+    return load_library("mb_gated_delta", ["gated_delta.cu"])
+
+
+CONV_ACTIVATIONS = {None: 0, "silu": 1}
+
+
+def _state_rows(state: torch.Tensor, offset: int, floats: int, name: str):
+    """The address and the row stride of the part of a per-sequence state [slots, n] float32 that starts `offset` floats in."""
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or offset < 0 or offset + floats > state.shape[1]:
+        raise KernelError(f"{name}: the state must be contiguous float32 [slots, n] with {floats} floats from {offset} on in every row")
+    return ctypes.c_void_p(state.data_ptr() + 4 * offset), ctypes.c_size_t(state.shape[1])
+
+
+def short_conv(x: torch.Tensor, weights: torch.Tensor, state: torch.Tensor, state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor,
+               max_q_len: int, in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None,
+               activation: Optional[str] = None) -> torch.Tensor:
+    """A short causal convolution over time per channel: with x_t = x[t] (+ in_bias) and `weights` [channels, taps] whose last
+    column meets the current token, out[t] = act(sum_i weights[:, taps - 1 - i] * x_(t - i) (+ out_bias)) as float32
+    [tokens, channels].  The inputs before a step's first token come from the sequence's tail, [taps - 1, channels] float32 at
+    `state_offset` floats into its row of `state` (zeros for a new sequence); `short_conv_tail` stores the new tail."""
+    _cuda(x, weights, state, slots, cu_q, in_bias, out_bias)
+    _int32(slots, "slots")
+    _int32(cu_q, "cu_q")
+    _columns(x, "x")
+    channels, taps = weights.shape
+    if x.shape[1] != channels or weights.dtype != torch.float32 or not weights.is_contiguous():
+        raise KernelError(f"short_conv: float32 weights [channels, taps] must fit rows of {x.shape[1]} channels, got {tuple(weights.shape)} {weights.dtype}")
+    for name, t in (("in_bias", in_bias), ("out_bias", out_bias)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != channels or not t.is_contiguous()):
+            raise KernelError(f"short_conv: {name} must be contiguous float32 of {channels} elements")
+    if activation not in CONV_ACTIVATIONS:
+        raise KernelError(f"short_conv: activation {activation!r} is not built (known: silu or none)")
+    tail, stride = _state_rows(state, state_offset, (taps - 1) * channels, "short_conv")
+    out = torch.empty((x.shape[0], channels), dtype=torch.float32, device=x.device)
+    lib = gated_delta_library()
+    _run(lib, lib.mb_short_conv(_p(x), x.stride(0), _code(x.dtype), _p(in_bias), _p(weights), _p(out_bias), CONV_ACTIVATIONS[activation],
+                                _p(out), out.stride(0), tail, stride, _p(slots), _p(cu_q), cu_q.numel() - 1, max_q_len, channels, taps,
+                                _stream()))
+    return out
+
+
+def short_conv_tail(x: torch.Tensor, taps: int, state: torch.Tensor, state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor,
+                    in_bias: Optional[torch.Tensor] = None) -> None:
+    """Stores every sequence's new tail: its last taps - 1 inputs x (+ in_bias), from the step's rows and, where the step brought
+    fewer, from the old tail.  To be called after `short_conv` has read the old one."""
+    _cuda(x, state, slots, cu_q, in_bias)
+    _columns(x, "x")
+    channels = x.shape[1]
+    tail, stride = _state_rows(state, state_offset, (taps - 1) * channels, "short_conv_tail")
+    lib = gated_delta_library()
+    _run(lib, lib.mb_short_conv_tail(_p(x), x.stride(0), _code(x.dtype), _p(in_bias), tail, stride, _p(slots), _p(cu_q),
+                                     cu_q.numel() - 1, channels, taps, _stream()))
+
+
+def gated_delta_scan(conv: torch.Tensor, q_at: int, k_at: int, v_at: int, a_in: torch.Tensor, b_in: torch.Tensor, gate_in: torch.Tensor,
+                     decay: torch.Tensor, dt_bias: torch.Tensor, gain: torch.Tensor, unit_eps: float, eps: float, state: torch.Tensor,
+                     state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                     out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """The gated delta rule over the new tokens of every sequence.  `conv` float32 [tokens, n] holds the convolved q (kv_heads
+    heads of `dim` from column q_at), k (from k_at) and v (heads heads of `vdim` from v_at); q and k become unit vectors
+    x / sqrt(sum x^2 + unit_eps), q times dim^-1/2; beta = sigmoid(b_in), g = exp(decay * softplus(a_in + dt_bias)) per head
+    (decay = -exp(A_log)); per head, from the sequence's float32 state S [heads, dim, vdim] at `state_offset` floats into its
+    row of `state` (updated in place): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = out_scale * o / rms(o)
+    * gain * silu(gate_in), rms over the head (eps `eps`).  a_in, b_in [tokens, heads], gate_in and out [tokens, heads * vdim]
+    are column slices; a_in, b_in and gate_in share one row stride."""
+    _cuda(conv, a_in, b_in, gate_in, decay, dt_bias, gain, state, slots, cu_q, out)
+    _int32(slots, "slots")
+    _int32(cu_q, "cu_q")
+    tokens = conv.shape[0]
+    if conv.dtype != torch.float32 or conv.stride(1) != 1 or max(q_at, k_at) + kv_heads * dim > conv.shape[1] or v_at + heads * vdim > conv.shape[1]:
+        raise KernelError(f"gated_delta_scan: the convolved rows {tuple(conv.shape)} {conv.dtype} do not hold the q, k and v parts")
+    for name, t, width in (("a_in", a_in, heads), ("b_in", b_in, heads), ("gate_in", gate_in, heads * vdim), ("out", out, heads * vdim)):
+        _columns(t, name)
+        if tuple(t.shape) != (tokens, width) or t.dtype != out.dtype:
+            raise KernelError(f"gated_delta_scan: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {out.dtype} is needed")
+    if not (a_in.stride(0) == b_in.stride(0) == gate_in.stride(0)):
+        raise KernelError("gated_delta_scan: a_in, b_in and gate_in must share one row stride")
+    for name, t, n in (("decay", decay, heads), ("dt_bias", dt_bias, heads), ("gain", gain, vdim)):
+        if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+            raise KernelError(f"gated_delta_scan: {name} must be contiguous float32 of {n} elements")
+    rows, stride = _state_rows(state, state_offset, heads * dim * vdim, "gated_delta_scan")
+    lib = gated_delta_library()
+    _run(lib, lib.mb_gated_delta_scan(_p(conv), conv.stride(0), _p(a_in), _p(b_in), _p(gate_in), a_in.stride(0), _code(out.dtype), _p(decay),
+                                      _p(dt_bias), _p(gain), ctypes.c_float(unit_eps), ctypes.c_float(eps), rows, stride, _p(slots),
+                                      _p(cu_q), cu_q.numel() - 1, _p(out), out.stride(0), ctypes.c_float(out_scale), heads, kv_heads, dim,
+                                      vdim, q_at, k_at, v_at, _stream()))
+
+
+def rglru_scan(gates: torch.Tensor, per: int, u: torch.Tensor, y_in: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor,
+               y_bias: torch.Tensor, rate: torch.Tensor, state: torch.Tensor, state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor,
+               max_q_len: int, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """The real-gated linear recurrent unit over the new tokens of every sequence: with r = sigmoid(r_sum + r_bias),
+    i = sigmoid(i_sum + i_bias), a = exp(rate * r) (rate <= 0 per channel): S = a S + sqrt(1 - a^2) * i * u from the sequence's
+    float32 state [width] at `state_offset` floats into its row of `state` (updated in place); out = out_scale * S *
+    gelu_tanh(y_in + y_bias).  `gates` float32 [tokens, 2 * width] holds the sums block by block of `per` channels: the r sums
+    of block 0, its i sums, the r sums of block 1, ...; u float32 [tokens, width]; y_in and out column slices."""
+    _cuda(gates, u, y_in, r_bias, i_bias, y_bias, rate, state, slots, cu_q, out)
+    _int32(slots, "slots")
+    _int32(cu_q, "cu_q")
+    tokens, width = u.shape
+    if gates.dtype != torch.float32 or u.dtype != torch.float32 or gates.stride(1) != 1 or u.stride(1) != 1 or tuple(gates.shape) != (tokens, 2 * width):
+        raise KernelError(f"rglru_scan: gates {tuple(gates.shape)} and u {tuple(u.shape)} must be float32 [tokens, 2 * width] and [tokens, width]")
+    for name, t in (("y_in", y_in), ("out", out)):
+        _columns(t, name)
+        if tuple(t.shape) != (tokens, width) or t.dtype != out.dtype:
+            raise KernelError(f"rglru_scan: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {out.dtype} is needed")
+    for name, t in (("r_bias", r_bias), ("i_bias", i_bias), ("y_bias", y_bias), ("rate", rate)):
+        if t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous():
+            raise KernelError(f"rglru_scan: {name} must be contiguous float32 of {width} elements")
+    rows, stride = _state_rows(state, state_offset, width, "rglru_scan")
+    lib = gated_recurrence_library()
+    _run(lib, lib.mb_rglru_scan(_p(gates), gates.stride(0), int(per), _p(u), u.stride(0), _p(y_in), y_in.stride(0), _code(out.dtype),
+                                _p(r_bias), _p(i_bias), _p(y_bias), _p(rate), rows, stride, _p(slots), _p(cu_q), cu_q.numel() - 1,
+                                max_q_len, width, _p(out), out.stride(0), ctypes.c_float(out_scale), _stream()))
 
 
 def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim):
@@ -1579,10 +1792,16 @@ def routed_experts_library():
     return load_library("mb_routed_experts", ["routed_experts.cu"])
 
 
-def router_topk(x: torch.Tensor, router: torch.Tensor, top: int):
+def router_topk(x: torch.Tensor, router: torch.Tensor, top: int, scored: bool = False, correction: Optional[torch.Tensor] = None,
+                groups: int = 1, keep: int = 1, weight_scale: float = 1.0):
     """Router logits z = router . x in float32 sums; per token the `top` experts with the largest logits (ties to the lower
-    index) as int32 [tokens, top], largest first, and the softmax over the chosen logits as float32 [tokens, top]."""
-    _cuda(x, router)
+    index) as int32 [tokens, top], largest first, and the softmax over the chosen logits as float32 [tokens, top].
+    `scored`: the scores s = softmax(z) over all experts are taken first; the choice runs on s + correction (float32
+    [experts], or None); the experts form `groups` equal groups of neighbours, a group counts by its largest choice score and
+    only the `keep` best groups' experts can be chosen; the weights are weight_scale * s of the chosen, not renormalised."""
+    _cuda(x, router, correction)
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != router.shape[0] or not correction.is_contiguous()):
+        raise KernelError(f"router_topk: the correction must be contiguous float32 of {router.shape[0]} elements")
     _columns(x, "x")
     if router.dim() != 2 or not router.is_contiguous() or router.dtype != x.dtype or router.shape[1] != x.shape[1]:
         raise KernelError(f"router_topk: the router {tuple(router.shape)} {router.dtype} does not fit rows {tuple(x.shape)} {x.dtype}")
@@ -1591,7 +1810,7 @@ def router_topk(x: torch.Tensor, router: torch.Tensor, top: int):
     weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
     lib = routed_experts_library()
     _run(lib, lib.mb_router_topk(_p(x), x.stride(0), _p(router), _code(x.dtype), _p(chosen), _p(weights), tokens, x.shape[1], experts,
-                                 top, _stream()))
+                                 top, 1 if scored else 0, _p(correction), int(groups), int(keep), ctypes.c_float(weight_scale), _stream()))
     return chosen, weights
 
 
@@ -1628,7 +1847,7 @@ def _expert_weights(w: torch.Tensor, experts: int, name: str):
 
 
 def expert_first_product(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, plan: RoutePlan, limit: float, slope: float,
-                         tensor_cores: bool = True) -> torch.Tensor:
+                         tensor_cores: bool = True, up_offset: float = 1.0) -> torch.Tensor:
     """mid [entries, n] (rows in the plan's sorted order, x's dtype): for every entry of expert e and its token's row x,
     g = min(gate_w[e] . x, limit), u = clamp(up_w[e] . x, -limit, limit), mid = g * sigmoid(slope * g) * (u + 1)."""
     _cuda(x, gate_w, up_w)
@@ -1642,7 +1861,7 @@ def expert_first_product(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tens
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_product(_p(x), x.stride(0), _p(gate_w), _p(up_w), _p(mid), None, n, _code(x.dtype), _p(plan.sorted),
                                     _p(plan.offsets), _p(plan.tile_expert), _p(plan.tile_row), plan.max_tiles, plan.top, n, k,
-                                    ctypes.c_float(limit), ctypes.c_float(slope), 1, 1 if tensor_cores else 0, _stream()))
+                                    ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(up_offset), 1, 1 if tensor_cores else 0, _stream()))
     return mid
 
 
@@ -1657,7 +1876,7 @@ def expert_second_product(mid: torch.Tensor, down_w: torch.Tensor, plan: RoutePl
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_product(_p(mid), mid.stride(0), _p(down_w), None, None, _p(slot_out), n, _code(mid.dtype), _p(plan.sorted),
                                     _p(plan.offsets), _p(plan.tile_expert), _p(plan.tile_row), plan.max_tiles, plan.top, n, k,
-                                    ctypes.c_float(0.0), ctypes.c_float(0.0), 0, 1 if tensor_cores else 0, _stream()))
+                                    ctypes.c_float(0.0), ctypes.c_float(0.0), ctypes.c_float(0.0), 0, 1 if tensor_cores else 0, _stream()))
     return slot_out
 
 
@@ -1719,7 +1938,8 @@ def grouped_product_takes(gate_up: torch.Tensor, down: torch.Tensor) -> bool:
             and down.data_ptr() % 16 == 0 and 2 * experts * ff < 2 ** 31 and route_pad_takes(experts))
 
 
-def grouped_first_product(a: torch.Tensor, gate_up: torch.Tensor, plan: PaddedRoutePlan, limit: float, slope: float) -> torch.Tensor:
+def grouped_first_product(a: torch.Tensor, gate_up: torch.Tensor, plan: PaddedRoutePlan, limit: float, slope: float,
+                          up_offset: float = 1.0) -> torch.Tensor:
     """mid bfloat16 [plan.rows, ff]: for the rows of a tile of expert e, g = min(gate[e] . a, limit),
     u = clamp(up[e] . a, -limit, limit), mid = g * sigmoid(slope * g) * (u + 1), on the tcgen05 tensor cores."""
     _cuda(a, gate_up)
@@ -1729,7 +1949,7 @@ def grouped_first_product(a: torch.Tensor, gate_up: torch.Tensor, plan: PaddedRo
     mid = torch.empty((plan.rows, ff), dtype=torch.bfloat16, device=a.device)
     lib = gemm_tc()
     _run(lib, lib.mb_gemm_tcgen05_grouped(_p(a), a.stride(0), _p(gate_up), width, 2 * experts * ff, _p(mid), ff, plan.rows, ff, width,
-                                          1, experts * ff, _p(plan.tile_group), ctypes.c_float(limit), ctypes.c_float(slope),
+                                          1, experts * ff, _p(plan.tile_group), ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(up_offset),
                                           _sm_count(a.device), _stream()))
     return mid
 
@@ -1743,7 +1963,7 @@ def grouped_second_product(mid: torch.Tensor, down: torch.Tensor, plan: PaddedRo
     out = torch.empty((plan.rows, width), dtype=torch.float32, device=mid.device)
     lib = gemm_tc()
     _run(lib, lib.mb_gemm_tcgen05_grouped(_p(mid), ff, _p(down), ff, experts * width, _p(out), width, plan.rows, width, ff, 0, 0,
-                                          _p(plan.tile_group), ctypes.c_float(0.0), ctypes.c_float(0.0), _sm_count(mid.device),
+                                          _p(plan.tile_group), ctypes.c_float(0.0), ctypes.c_float(0.0), ctypes.c_float(0.0), _sm_count(mid.device),
                                           _stream()))
     return out
 
@@ -1754,7 +1974,7 @@ EXPERT_ROWS_ENTRIES = 64  # up to so many (token, choice) entries a step's exper
 
 
 def expert_rows_first(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, chosen: torch.Tensor, limit: float,
-                      slope: float) -> torch.Tensor:
+                      slope: float, up_offset: float = 1.0) -> torch.Tensor:
     """The first product for a step of few tokens: mid [tokens * top, n] (row token * top + choice, x's dtype), each row
     clamped_swish(gate_w[e] . x, up_w[e] . x) for its token's row x and its chosen expert e.  Every entry streams its
     expert's matrices once; nothing is sorted."""
@@ -1772,7 +1992,7 @@ def expert_rows_first(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor,
     mid = torch.empty((chosen.numel(), n), dtype=x.dtype, device=x.device)
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_rows(_p(x), x.stride(0), _p(gate_w), _p(up_w), _p(mid), None, n, _code(x.dtype), _p(chosen), chosen.numel(),
-                                 top, experts, n, k, ctypes.c_float(limit), ctypes.c_float(slope), 1, _stream()))
+                                 top, experts, n, k, ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(up_offset), 1, _stream()))
     return mid
 
 
@@ -1789,11 +2009,11 @@ def expert_rows_second(mid: torch.Tensor, down_w: torch.Tensor, chosen: torch.Te
     slot_out = torch.empty((mid.shape[0], n), dtype=torch.float32, device=mid.device)
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_rows(_p(mid), mid.stride(0), _p(down_w), None, None, _p(slot_out), n, _code(mid.dtype), _p(chosen),
-                                 chosen.numel(), chosen.shape[1], experts, n, k, ctypes.c_float(0.0), ctypes.c_float(0.0), 0, _stream()))
+                                 chosen.numel(), chosen.shape[1], experts, n, k, ctypes.c_float(0.0), ctypes.c_float(0.0), ctypes.c_float(0.0), 0, _stream()))
     return slot_out
 
 
-def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> None:
+def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, up_offset: float = 1.0) -> None:
     """out = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and up column
     slices of one tensor."""
     _cuda(gate, up, out)
@@ -1803,15 +2023,18 @@ def clamped_swish(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, limit
         raise KernelError("clamped_swish: gate, up and out must share shape and dtype, gate and up one row stride")
     lib = routed_experts_library()
     _run(lib, lib.mb_clamped_swish(_p(gate), _p(up), gate.stride(0), _p(out), out.stride(0), _code(gate.dtype), gate.shape[0],
-                                   gate.shape[1], ctypes.c_float(limit), ctypes.c_float(slope), _stream()))
+                                   gate.shape[1], ctypes.c_float(limit), ctypes.c_float(slope), ctypes.c_float(up_offset), _stream()))
 
 
 def expert_combine(slot_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
-                   score: Optional[torch.Tensor] = None, position: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   score: Optional[torch.Tensor] = None, position: Optional[torch.Tensor] = None,
+                   chosen: Optional[torch.Tensor] = None, experts: int = 0, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = sum_s weights[t, s] * slot_out[t * top + s] (+ sigmoid(score[t]) * shared[t]) as float32 [tokens, width];
-    shared float32 [tokens, width], score one number per token ([tokens, 1], may be a column slice).  With `position`
-    (int32 [tokens * top]) entry t * top + s has its row of slot_out at position[t * top + s]."""
-    _cuda(slot_out, weights, shared, score, position)
+    shared float32 [tokens, width], score one number per token ([tokens, 1], may be a column slice; None: the shared expert
+    is added as it is).  With `position` (int32 [tokens * top]) entry t * top + s has its row of slot_out at
+    position[t * top + s].  With `chosen` (int32 [tokens, top]), `experts` and `rows` ([tokens, width], the rows the experts
+    read): an entry whose expert is >= `experts` is an identity expert, its result is rows[t] and slot_out is not read for it."""
+    _cuda(slot_out, weights, shared, score, position, chosen, rows)
     tokens, top = weights.shape
     width = slot_out.shape[1]
     if position is not None and (position.dtype != torch.int32 or position.numel() != tokens * top or not position.is_contiguous()):
@@ -1819,15 +2042,30 @@ def expert_combine(slot_out: torch.Tensor, weights: torch.Tensor, shared: Option
     if slot_out.dtype != torch.float32 or not slot_out.is_contiguous() or (position is None and slot_out.shape[0] != tokens * top) \
             or weights.dtype != torch.float32 or not weights.is_contiguous():
         raise KernelError("expert_combine: slot_out float32 [tokens * top, width] and weights float32 [tokens, top] are needed")
-    if (shared is None) != (score is None):
-        raise KernelError("expert_combine: a shared expert and its gate scores come together")
+    if score is not None and shared is None:
+        raise KernelError("expert_combine: gate scores without a shared expert")
+    dtype = _F32
     if shared is not None:
-        _columns(score, "score")
-        if shared.dtype != torch.float32 or not shared.is_contiguous() or tuple(shared.shape) != (tokens, width) or score.shape[0] != tokens:
-            raise KernelError("expert_combine: shared must be contiguous float32 [tokens, width] with one score per token")
+        if shared.dtype != torch.float32 or not shared.is_contiguous() or tuple(shared.shape) != (tokens, width):
+            raise KernelError("expert_combine: shared must be contiguous float32 [tokens, width]")
+        if score is not None:
+            _columns(score, "score")
+            if score.shape[0] != tokens:
+                raise KernelError("expert_combine: one gate score per token is needed")
+            dtype = _code(score.dtype)
+    if (chosen is None) != (rows is None):
+        raise KernelError("expert_combine: identity experts need both the choices and the tokens' rows")
+    if chosen is not None:
+        _int32(chosen, "chosen")
+        _columns(rows, "rows")
+        if tuple(chosen.shape) != (tokens, top) or not chosen.is_contiguous() or tuple(rows.shape) != (tokens, width):
+            raise KernelError("expert_combine: choices [tokens, top] and rows [tokens, width] are needed")
+        if score is not None and score.dtype != rows.dtype:
+            raise KernelError("expert_combine: gate scores and rows must share one dtype")
+        dtype = _code(rows.dtype)
     out = torch.empty((tokens, width), dtype=torch.float32, device=slot_out.device)
     lib = routed_experts_library()
     _run(lib, lib.mb_expert_combine(_p(slot_out), _p(weights), _p(shared), _p(score), score.stride(0) if score is not None else 0,
-                                    _code(score.dtype) if score is not None else _F32, _p(out), tokens, width, top, _p(position),
-                                    _stream()))
+                                    dtype, _p(out), tokens, width, top, _p(position), _p(chosen), int(experts), _p(rows),
+                                    rows.stride(0) if rows is not None else 0, _stream()))
     return out

@@ -109,10 +109,19 @@ class StreamsRead:
     reader: object
 
 
+@dataclass
+class StreamRows:
+    """What a block whose sublayers read the stream itself may hand on: the stream is up to date, and `rows` holds its rows in
+    the compute type, stored by the kernel that made the last addition; `reader` is the block they were left for."""
+
+    rows: torch.Tensor
+    reader: object
+
+
 def as_delta(pending):
-    """The delta that is still to be added into the residual stream, or None (also for a Prenormed or a StreamsRead:
-    the stream they belong to is up to date)."""
-    return None if isinstance(pending, (Prenormed, StreamsRead)) else pending
+    """The delta that is still to be added into the residual stream, or None (also for a Prenormed, a StreamsRead or a
+    StreamRows: the stream they belong to is up to date)."""
+    return None if isinstance(pending, (Prenormed, StreamsRead, StreamRows)) else pending
 
 
 class Part:

@@ -113,6 +113,24 @@ class GatedFeedForward(Part):
         _, gained, ssq, count = product(hidden, self.w_down, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
         return Prenormed(gained, ssq, count, x.shape[1], next_norm.spec.eps, next_norm)
 
+    def forward_wide(self, xn: torch.Tensor, batch=None, run=None) -> torch.Tensor:
+        """down(act(gate(xn)) * up(xn)) as the float32 sums of the down product, for a block that norms a sublayer's result
+        before it meets the stream."""
+        rows = xn.shape[0]
+        if self.b_gate_up is None and xn.dtype == torch.bfloat16 and ops.skinny_pays(self.w_gate_up, rows):
+            hidden = ops.skinny_gemm(self.w_gate_up, self.gated, x=xn)
+        elif self.b_gate_up is None and xn.dtype == torch.bfloat16 and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows):
+            hidden = ops.tensor_core_gemm(xn, self.w_gate_up, self.gated)
+        else:
+            gate_up = linear(xn, self.w_gate_up, self.runtime.compute_dtype)
+            if self.b_gate_up is not None:
+                ops.bias_add(gate_up, self.b_gate_up)
+            hidden = ops.swiglu(gate_up, self.spec.activation)
+        out = linear(hidden, self.w_down, torch.float32)
+        if self.b_down is not None:
+            ops.bias_add(out, self.b_down)
+        return out
+
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
         if self.b_gate_up is None and ops.skinny_pays(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:

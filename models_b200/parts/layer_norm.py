@@ -1,4 +1,4 @@
-"""Layer norm with gain and bias: (x - mean) / sqrt(variance + eps) * weight + bias, the variance being
+"""Layer norm with a gain and (unless the spec says there is none) a bias: (x - mean) / sqrt(variance + eps) * weight + bias, the variance being
 the mean of the squared deviations from the mean; all of it in float32 on the float32 residual stream.
 """
 
@@ -19,12 +19,13 @@ class LayerNorm(Part):
 
     def parameters(self):
         n = self.spec.weights
-        return [ParamRequest(n["weight"], (self.spec.size,), "gain"), ParamRequest(n["bias"], (self.spec.size,), "bias")]
+        out = [ParamRequest(n["weight"], (self.spec.size,), "gain")]
+        return out + [ParamRequest(n["bias"], (self.spec.size,), "bias")] if getattr(self.spec, "bias", True) else out
 
     def load(self, tensors):
         n = self.spec.weights
         self.weight = self.runtime.vector(tensors[n["weight"]])
-        self.bias = self.runtime.vector(tensors[n["bias"]])
+        self.bias = self.runtime.vector(tensors[n["bias"]]) if getattr(self.spec, "bias", True) else None
 
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
                 write_x: bool = True) -> torch.Tensor:

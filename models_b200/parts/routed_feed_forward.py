@@ -5,6 +5,13 @@ is a gated feed-forward with clamped branches, g = min(Wg.xn, limit), u = clamp(
 Wd.(g * sigmoid(slope * g) * (u + 1)).  A shared expert of the same form (sizes and limit of its own) runs for every token
 and is added multiplied by sigmoid(w.xn), one number per token.
 
+Variations the spec may ask for.  A "scored" rule: the scores s = softmax(z) run over ALL router outputs, the choice runs on
+s + correction (a tensor), restricted to the outputs of the `keep_groups` best of `groups` equal groups of neighbouring outputs
+(a group counts by its largest choice score), and the weights are weight_scale * s of the chosen, not renormalised.  Identity
+experts: the router's last outputs stand for experts without tensors whose result is their input; their entries skip both
+products and enter the weighted sum as the token's own row.  An expert without clamps and without the one added to the up
+branch (limit +inf, slope 1, up_offset 0: silu(g) * u).  A shared expert that is added as it is, without a gate.
+
 The step's (token, choice) entries are sorted by expert on the device; the experts' two products are then grouped products
 over the sorted rows (a block a tile of one expert's rows), whose grids depend on the number of tokens only -- nothing comes
 back to the host, so a step can be captured.  A prompt with enough rows per expert pads every expert's rows to whole tiles
@@ -27,8 +34,15 @@ from .registry import register_part
 class RoutedFeedForward(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
-        if not 1 <= spec.top <= spec.num_experts:
-            raise ValueError(f"top {spec.top} of {spec.num_experts} experts")
+        self.outputs = spec.num_experts + spec.identity_experts  # what the router has: experts, then identity experts
+        if not 1 <= spec.top <= self.outputs:
+            raise ValueError(f"top {spec.top} of {self.outputs} router outputs")
+        if spec.rule not in ("top_logits", "scored"):
+            raise ValueError(f"router rule {spec.rule!r} is not built (known: top_logits, scored)")
+        if spec.rule != "scored" and (spec.correction or spec.groups != 1 or spec.weight_scale != 1.0):
+            raise ValueError("a correction, groups and a weight scale belong to the scored rule")
+        if self.outputs % spec.groups or not 1 <= spec.keep_groups <= spec.groups:
+            raise ValueError(f"{spec.groups} groups (keeping {spec.keep_groups}) do not cut {self.outputs} router outputs evenly")
 
     def _expert_names(self, role: str):
         return [self.spec.weights["expert_" + role].format(expert=e) for e in range(self.spec.num_experts)]
@@ -36,18 +50,23 @@ class RoutedFeedForward(Part):
     def parameters(self):
         s, n = self.spec, self.spec.weights
         ff, W = s.expert.intermediate_size, s.hidden_size
-        out = [ParamRequest(n["router"], (s.num_experts, W))]
+        out = [ParamRequest(n["router"], (self.outputs, W))]
+        if s.correction:
+            out.append(ParamRequest(n["correction"], (self.outputs,), "bias"))
         for role, shape in (("gate", (ff, W)), ("up", (ff, W)), ("down", (W, ff))):
             out += [ParamRequest(name, shape) for name in self._expert_names(role)]
         if s.shared is not None:
             f = s.shared.intermediate_size
             out += [ParamRequest(n["shared_gate"], (f, W)), ParamRequest(n["shared_up"], (f, W)),
-                    ParamRequest(n["shared_down"], (W, f)), ParamRequest(n["shared_gate_score"], (1, W))]
+                    ParamRequest(n["shared_down"], (W, f))]
+            if s.shared_gated:
+                out.append(ParamRequest(n["shared_gate_score"], (1, W)))
         return out
 
     def load(self, tensors):
         s, n, rt = self.spec, self.spec.weights, self.runtime
         self.router = rt.matrix(tensors[n["router"]])
+        self.correction = rt.vector(tensors[n["correction"]]) if s.correction else None
         stacked = {}
         for role in ("gate", "up", "down"):
             parts = [rt.matrix(tensors[name]) for name in self._expert_names(role)]
@@ -64,7 +83,7 @@ class RoutedFeedForward(Part):
         self.grouped = self.w_gate_up.is_cuda and ops.grouped_product_takes(self.w_gate_up, self.w_down)
         self.shared_in = None
         if s.shared is not None:
-            first = [rt.matrix(tensors[n[r]]) for r in ("shared_gate", "shared_up", "shared_gate_score")]
+            first = [rt.matrix(tensors[n[r]]) for r in ("shared_gate", "shared_up") + (("shared_gate_score",) if s.shared_gated else ())]
             if len({m.dtype for m in first}) > 1:
                 first = [m.float() for m in first]
             self.shared_in, self.shared_starts = stack_rows(first)
@@ -73,31 +92,38 @@ class RoutedFeedForward(Part):
     def forward_wide(self, xn: torch.Tensor, batch=None, run=None) -> torch.Tensor:
         """float32 [tokens, width]."""
         s = self.spec
+        e = s.expert
         x = xn if xn.dtype == self.router.dtype else xn.to(self.router.dtype)
-        chosen, weights = ops.router_topk(x, self.router, s.top)
+        chosen, weights = ops.router_topk(x, self.router, s.top, scored=s.rule == "scored", correction=self.correction,
+                                          groups=s.groups, keep=s.keep_groups, weight_scale=s.weight_scale)
         position = None
+        # (an identity expert's id lies beyond the experts': the sorting and the products leave its entries out, and the
+        # weighted sum takes the token's own row for them)
         if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
             # a decode step: every entry streams its expert's matrices; no sorting, no tiles of mostly empty rows
-            mid = ops.expert_rows_first(x, self.w_gate, self.w_up, chosen, s.expert.limit, s.expert.swish_slope)
+            mid = ops.expert_rows_first(x, self.w_gate, self.w_up, chosen, e.limit, e.swish_slope, e.up_offset)
             slot_out = ops.expert_rows_second(mid, self.w_down, chosen)
         elif self.grouped and chosen.numel() >= ops.GROUPED_ROWS_PER_EXPERT * s.num_experts:
             # a prompt: every expert's rows fill tiles of their own, and both products run on the tcgen05 tensor cores
             plan = ops.route_pad(chosen, s.num_experts)
-            mid = ops.grouped_first_product(ops.gather_rows(x, plan), self.w_gate_up, plan, s.expert.limit, s.expert.swish_slope)
+            mid = ops.grouped_first_product(ops.gather_rows(x, plan), self.w_gate_up, plan, e.limit, e.swish_slope, e.up_offset)
             slot_out, position = ops.grouped_second_product(mid, self.w_down, plan), plan.position
         else:
             plan = ops.route_sort(chosen, s.num_experts)
-            mid = ops.expert_first_product(x, self.w_gate, self.w_up, plan, s.expert.limit, s.expert.swish_slope)
+            mid = ops.expert_first_product(x, self.w_gate, self.w_up, plan, e.limit, e.swish_slope, up_offset=e.up_offset)
             slot_out = ops.expert_second_product(mid, self.w_down, plan)
+        identity = dict(chosen=chosen, experts=s.num_experts, rows=x) if s.identity_experts else {}
         if self.shared_in is None:
-            return ops.expert_combine(slot_out, weights, position=position)
+            return ops.expert_combine(slot_out, weights, position=position, **identity)
         dtype = self.runtime.compute_dtype
         proj = linear(xn, self.shared_in, dtype)
         f, at = s.shared.intermediate_size, self.shared_starts
         shared_mid = torch.empty((xn.shape[0], f), dtype=dtype, device=xn.device)
-        ops.clamped_swish(proj[:, at[0]:at[0] + f], proj[:, at[1]:at[1] + f], shared_mid, s.shared.limit, s.shared.swish_slope)
+        ops.clamped_swish(proj[:, at[0]:at[0] + f], proj[:, at[1]:at[1] + f], shared_mid, s.shared.limit, s.shared.swish_slope,
+                          s.shared.up_offset)
         shared = linear(shared_mid, self.shared_down, torch.float32)
-        return ops.expert_combine(slot_out, weights, shared, proj[:, at[2]:at[2] + 1], position)
+        score = proj[:, at[2]:at[2] + 1] if s.shared_gated else None
+        return ops.expert_combine(slot_out, weights, shared, score, position, **identity)
 
     def forward(self, xn: torch.Tensor, batch=None, run=None) -> torch.Tensor:
         out = self.forward_wide(xn, batch, run)
