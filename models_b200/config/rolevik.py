@@ -81,7 +81,7 @@ class RolevikAttention:
     scale: float
     chunk: int  # 0: no "mask", every earlier key is visible
     rot_dims: int  # 0: no rotation
-    rot_base: float
+    rot_base: float  # 0: the layer has no "rot" at all
 
 
 @dataclass(frozen=True)
@@ -223,7 +223,7 @@ class RolevikConfig:
                 left = {"heads": a.heads, "kv_heads": a.kv_heads, "dim": a.dim, "vdim": a.vdim, "scale": a.scale}
                 if a.chunk:
                     left["mask"] = {"size": a.chunk}
-                if a.rot_dims:
+                if a.rot_base:
                     left["rot"] = {"dims": a.rot_dims, "base": a.rot_base}
                 mixer = {"left": left,
                          "right": {"heads": d.heads, "kv_heads": d.kv_heads, "dim": d.dim, "vdim": d.vdim, "conv": d.conv}}

@@ -422,7 +422,7 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
             weight = visible ? sigmoid(score) : 0.0f;
         }
         const int last = (pos - chunk < 31) ? pos - chunk : 31;
-        for (int jj = 0; jj <= last; ++jj) {
+        for (int jj = max(0, lowest - chunk); jj <= last; ++jj) {  // (keys before the first visible one are not read at all)
             const float w = __shfl_sync(0xffffffffu, weight, jj);
             const T* v_row = v_pool + (base + jj) * v_width;
 #pragma unroll
@@ -599,7 +599,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         // reads the run's last row again)
         constexpr int kAhead = kAcc <= 4 ? 8 : 4;
         const int last = min(31, end - 1 - chunk);
-        for (int j0 = 0; j0 <= last; j0 += kAhead) {
+        for (int j0 = max(0, lowest - chunk); j0 <= last; j0 += kAhead) {  // (from the first visible key on)
             float value[kAhead][kAcc];
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {

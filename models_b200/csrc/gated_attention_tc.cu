@@ -223,6 +223,20 @@ gated_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __rest
                 *reinterpret_cast<uint4*>(rows + (first_stale + i / kPieces) * kValueRow + (i % kPieces) * 16) = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
         }
+        if (t == t_begin && extras.block > 0) {
+            // The first tile may begin before the first key that any row of this block sees.  Those rows have weight 0 for
+            // every query, but 0 times a stray infinity or NaN is NaN, so their value rows are cleared too.
+            const int unseen = (pos0 / extras.block) * extras.block - key_base;
+            if (unseen > 0) {
+                unsigned char* rows = stage_smem + stage * kStageBytes + (kSharedRows ? 0 : kKeyTile);
+                constexpr int kPieces = kValueRow / 16;
+                if (!kSharedRows) {
+                    for (int i = threadIdx.x; i < unseen * kPieces; i += kThreads)
+                        *reinterpret_cast<uint4*>(rows + (i / kPieces) * kValueRow + (i % kPieces) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    __syncthreads();
+                }
+            }
+        }
         if (warp_has_rows && key_base <= warp_last && key_base + kTile > warp_first_low) {
             const bool full = key_base + kTile - 1 <= warp_first_pos && warp * 16 + 15 < valid && key_base >= warp_low;  // no mask needed
             float s[kTile / 8][4];

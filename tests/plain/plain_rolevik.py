@@ -16,6 +16,8 @@ import math
 
 import torch
 
+from .plain_llama import read_model_folder  # noqa: F401  (reads config.json and the safetensors file)
+
 F = torch.float64
 DELTA_UNIT_EPS = 1e-6  # the delta rule's unit vectors: x / sqrt(sum x^2 + 1e-6)
 RGLRU_RATE = 8.0       # log a = -8 r softplus(lam)
@@ -81,7 +83,7 @@ def chunked_attention(h, w, name, c, eps):
     q = rotate_half(q.view(T, H, D), positions, rot["dims"], rot["base"])
     k = rotate_half(k.view(T, G, D), positions, rot["dims"], rot["base"])
     v = v.view(T, G, Dv)
-    seen = chunk_visible(T, c["mask"]["size"])
+    seen = chunk_visible(T, c["mask"]["size"] if c.get("mask") else T)  # no mask: one chunk holds everything
     out = torch.zeros(T, H, Dv, dtype=F)
     for head in range(H):
         g = head // (H // G)
@@ -157,7 +159,8 @@ def gated_ff(h, w, name, act):
 
 def route(h, w, name, c):
     """(chosen [T, top], weights [T, top], margin [T]): the experts every token uses, the weights of their results, and how
-    far the last chosen choice score lies above the best one left out."""
+    clear the decision was: the smaller of (last chosen choice score - best one left out) and (last kept group's score - best
+    group left out), as a fraction of the spread of the token's choice scores."""
     r = c["router"]
     experts, identity, top = r["experts"], r.get("identity", 0), r["top"]
     total = experts + identity
@@ -167,13 +170,19 @@ def route(h, w, name, c):
     groups = r.get("groups") or {"count": 1, "keep": 1}
     per = total // groups["count"]
     best = choice.view(-1, groups["count"], per).max(-1).values
-    kept = torch.topk(best, groups["keep"], dim=-1).indices
+    by_group = torch.sort(best, dim=-1, descending=True)
+    kept = by_group.indices[:, :groups["keep"]]
     open_ = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
     masked = choice.masked_fill(~open_.repeat_interleave(per, dim=1), float("-inf"))
     ordered = torch.sort(masked, dim=-1, descending=True)
     chosen = ordered.indices[:, :top]
-    margin = ordered.values[:, top - 1] - ordered.values[:, top] if total > top else torch.full((h.shape[0],), float("inf"), dtype=F)
-    return chosen, torch.gather(s, 1, chosen) * r["scale"], margin
+    far = torch.full((h.shape[0],), float("inf"), dtype=F)
+    margin = ordered.values[:, top - 1] - ordered.values[:, top] if total > top else far
+    margin = torch.where(torch.isfinite(margin), margin, far)  # (everything left out lies in a closed group)
+    if groups["keep"] < groups["count"]:
+        margin = torch.minimum(margin, by_group.values[:, groups["keep"] - 1] - by_group.values[:, groups["keep"]])
+    spread = choice.std(-1).clamp_min(1e-30) if total > 1 else torch.ones_like(far)
+    return chosen, torch.gather(s, 1, chosen) * r["scale"], margin / spread
 
 
 def moe_ff(h, w, name, c):
@@ -188,14 +197,17 @@ def moe_ff(h, w, name, c):
     return out
 
 
-def feed_forward(h, w, name, c):
+def feed_forward(h, w, name, c, margins=None):
     if c["kind"] == "dense":
         return gated_ff(h, w, name, gelu_tanh)
+    if margins is not None:
+        margins.append(route(h, w, name, c)[2])
     return moe_ff(h, w, name, c)
 
 
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence (and, if asked, the stream after every layer [layers, T, W])."""
+def forward(config, w, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one sequence (and, if asked, the stream after every layer [layers, T, W]).  `margins` (a list)
+    receives, per layer with experts, how clear every token's router decision was (see `route`)."""
     eps = config["norm"]["eps"]
     table = f64(w["embed"])
     x = table[torch.as_tensor(tokens, dtype=torch.long)] * config["embedding"]["scale"]
@@ -210,7 +222,7 @@ def forward(config, w, tokens, return_layers=False):
             raise ValueError(layer["type"])
         x = x + f64(w[p + "ls1"]) * layer_norm(m, f64(w[p + "norm1"]), eps)
         if layer.get("mlp") is not None:
-            x = x + f64(w[p + "ls2"]) * layer_norm(feed_forward(x, w, p + "mlp.", layer["mlp"]), f64(w[p + "norm2"]), eps)
+            x = x + f64(w[p + "ls2"]) * layer_norm(feed_forward(x, w, p + "mlp.", layer["mlp"], margins), f64(w[p + "norm2"]), eps)
         layers.append(x.clone())
     logits = layer_norm(x, f64(w["final.norm"]), eps) @ table.T * config["logit_scale"]
     return (logits, torch.stack(layers)) if return_layers else logits
