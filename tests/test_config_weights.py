@@ -64,7 +64,7 @@ def test_bad_configs_are_refused_by_name(change, message):
 
 
 def test_registry_lists_what_is_built():
-    assert known_architectures() == ["Kabanex", "Kivezen", "LlamaForCausalLM", "Lovurax"]
+    assert known_architectures() == ["Kabanex", "Kivezen", "LlamaForCausalLM", "Lovurax", "Rolevik"]
     with pytest.raises(ConfigError, match="MistralForCausalLM.*LlamaForCausalLM"):
         config_from_dict(dict(TINY_A, architectures=["MistralForCausalLM"]))
     with pytest.raises(ConfigError, match="architectures"):
