@@ -776,6 +776,232 @@ def kivezen_kernels(z, peak, prompt=2048, batch=8, context=1536):
     return out
 
 
+# --design rolevik: the Rolevik decoder (layers with the norm on the sublayers' results; an attention over chunks beside a gated
+# delta rule; recurrent blocks around a gated linear recurrence; routed experts with a scored router, groups and identity
+# experts) beside a Kivezen of equal size: the model of this package whose layers are nearest (attention through the same paged
+# kernels, a recurrence with a matrix of state per head, routed experts); equal size counts the parameters a token uses.
+
+ROLEVIK_SIZES = {
+    # width, layers (ROLEVIK_ORDER in turn), the attention's heads, key/value heads, key size, value size and chunk, the delta
+    # rule's heads and query/key heads (same key and value sizes), the recurrent block's width and blocks, dense ff, experts,
+    # identity experts, chosen per token, groups (count, kept), an expert's ff, the shared expert's ff
+    "s": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=64, vdim=128, chunk=512, delta_heads=8, delta_kv_heads=4, recurrent=1024,
+              blocks=4, ff=2048, experts=16, identity=4, top=2, groups=(4, 2), expert_ff=512, shared_ff=512),
+    "m": dict(width=2048, layers=16, heads=16, kv_heads=4, dim=64, vdim=128, chunk=1024, delta_heads=16, delta_kv_heads=8, recurrent=2048,
+              blocks=8, ff=4096, experts=32, identity=8, top=4, groups=(8, 4), expert_ff=512, shared_ff=1024),
+}
+ROLEVIK_ORDER = (("parallel", "dense"), ("rglru", "moe"), ("parallel", "moe"), ("rglru", "dense"))
+
+
+def rolevik_config(z):
+    D, DV = z["dim"], z["vdim"]
+    mixers = {
+        "parallel": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": D, "vdim": DV, "scale": D ** -0.5,
+                              "mask": {"size": z["chunk"]}, "rot": {"dims": D // 2, "base": 500000.0}},
+                     "right": {"heads": z["delta_heads"], "kv_heads": z["delta_kv_heads"], "dim": D, "vdim": DV, "conv": 4}},
+        "rglru": {"width": z["recurrent"], "blocks": z["blocks"], "conv": 4},
+    }
+    mlps = {"dense": {"kind": "dense", "ff": z["ff"]},
+            "moe": {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+                    "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.5,
+                               "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}}
+    layers = []
+    for i in range(z["layers"]):
+        mixer, mlp = ROLEVIK_ORDER[i % 4]
+        layers.append({"type": mixer, "mixer": mixers[mixer], "mlp": mlps[mlp]})
+    return {"architecture": "Rolevik", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "layers": layers}
+
+
+def rolevik_layer_params(z):
+    """Matrix parameters a token uses in a layer (of the experts only the chosen ones and the shared one), averaged over the
+    four layers of a turn."""
+    w, h, g, d, dv, dh, dg, r = (z[k] for k in ("width", "heads", "kv_heads", "dim", "vdim", "delta_heads", "delta_kv_heads", "recurrent"))
+    mixer = {"parallel": w * (h * d + g * d + g * dv) + h * dv * w + w * (2 * dg * d + 2 * dh * dv + 2 * dh) + dh * dv * w,
+             "rglru": 3 * w * r + 2 * r * (r // z["blocks"])}
+    mlp = {"dense": 3 * w * z["ff"], "moe": z["top"] * 3 * w * z["expert_ff"] + 3 * w * z["shared_ff"] + w * (z["experts"] + z["identity"])}
+    return sum(mixer[a] + mlp[b] for a, b in ROLEVIK_ORDER) // 4
+
+
+def kivezen_of_equal_size(z):
+    """A Kivezen with one residual stream, of the same width, layers, heads, head sizes and experts, whose dense feed-forward
+    width (a multiple of 256) makes a layer's parameters equal to those a Rolevik token uses."""
+    zk = dict(z, streams=1, ff=0)
+    ff = max(256, round((rolevik_layer_params(z) - kivezen_layer_params(zk)) / z["width"] / 256) * 256)  # (half the layers are dense: 2 w ff / 2)
+    config = kivezen_config(dict(zk, ff=ff))
+    del config["streams"]  # a plain residual sum
+    return config
+
+
+def rolevik_kernels(z, peak, prompt=2048, batch=8, context=1536):
+    """The design's kernels alone beside the like kernels of the other models at equal sizes, each with its fraction of the
+    measured peak that bounds it."""
+    import torch
+
+    from models_b200.kernels import ops
+
+    dev, bf = "cuda", torch.bfloat16
+    H, G, D, DV, W = (z[k] for k in ("heads", "kv_heads", "dim", "vdim", "width"))
+    DH, DG, R, B = z["delta_heads"], z["delta_kv_heads"], z["recurrent"], z["blocks"]
+    E, I, top, F = z["experts"], z["identity"], z["top"], z["expert_ff"]
+    page, taps = 64, 4
+    out = {}
+
+    def paged(sequences, length, key, value):
+        pages = sequences * (-(-length // page))
+        k_pool = torch.randn((pages + 1, G, page, key), device=dev).to(bf)
+        v_pool = torch.randn((pages + 1, G, page, value), device=dev).to(bf)
+        table = (torch.arange(pages, dtype=torch.int32, device=dev) + 1).reshape(sequences, -1).contiguous()
+        return k_pool, v_pool, table
+
+    def rated(us, flops=None, moved=None):
+        if flops is not None:
+            return {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak["bf16_tflops"]}
+        return {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+
+    longest = max(prompt, context)
+    angle = torch.arange(longest, dtype=torch.float32, device=dev)[:, None]
+    cos, sin = (f(angle * torch.rand((1, D // 4), device=dev)).contiguous() for f in (torch.cos, torch.sin))  # D / 2 coordinates turn
+    vcos, vsin = (f(angle * torch.rand((1, DV // 2), device=dev)).contiguous() for f in (torch.cos, torch.sin))
+    temperature = torch.rand(H, device=dev) + 0.5
+    chunk = z["chunk"]
+    for name, rows, cu_q, lengths, q_len in (("prompt", prompt, [0, prompt], [prompt], prompt),
+                                             ("decode", batch, list(range(batch + 1)), [context] * batch, 1)):
+        sequences = len(lengths)
+        cu = torch.tensor(cu_q, dtype=torch.int32, device=dev)
+        kv = torch.tensor(lengths, dtype=torch.int32, device=dev)
+        slots = torch.arange(sequences, dtype=torch.int32, device=dev)
+        # (query, key) pairs of a head: inside the query's chunk only; in all for the attention without chunks beside it
+        seen = sum(p % chunk + 1 for n in lengths for p in range(n - q_len, n))
+        pairs = sum(sum(range(n - q_len + 1, n + 1)) for n in lengths)
+        positions = torch.cat([torch.arange(n - q_len, n) for n in lengths]).to(torch.int32).to(dev)
+        k_pool, v_pool, table = paged(sequences, lengths[0], D, DV)
+        q, o = torch.randn((rows, H * D), device=dev).to(bf), torch.empty((rows, H * DV), dtype=bf, device=dev)
+        us = time_kernel(lambda: ops.gated_attention(q, o, k_pool, v_pool, table, cu, kv, q_len, H, G, D, DV, "softmax", D ** -0.5, block=chunk))
+        out[f"{name}_chunked_attention"] = rated(us, flops=seen * H * (2 * D + 2 * DV)) if q_len > 1 else \
+            rated(us, moved=sum(n - 1 - (n - 1) // chunk * chunk + 1 for n in lengths) * G * (D + DV) * 2)
+        us = time_kernel(lambda: ops.gated_attention(q, o, k_pool, v_pool, table, cu, kv, q_len, H, G, D, DV, "softmax", D ** -0.5,
+                                                     head_scale=temperature, softcap=50.0, sink=True, turn_cos=vcos, turn_sin=vsin))
+        out[f"{name}_capped_attention_kivezen"] = rated(us, flops=pairs * H * (2 * D + 2 * DV)) if q_len > 1 else \
+            rated(us, moved=sum(lengths) * G * (D + DV) * 2)
+        # what stands before it: biases, one norm over each whole projection, rotation, the pools; beside Kivezen's kernel
+        qkv = torch.randn((rows, (H + G) * D + G * DV), device=dev).to(bf)
+        a, b = H * D, (H + G) * D
+        mapping = (torch.arange(rows, dtype=torch.int32, device=dev) + page)
+        moved = rows * (2 * H * D + 2 * G * D + 2 * G * DV) * 2
+        bq, bk, bv, gq, gk = (torch.randn(n, device=dev) for n in (H * D, G * D, G * DV, H * D, G * D))
+        us = time_kernel(lambda: ops.project_norm_rotate_store(qkv[:, :a], qkv[:, a:b], qkv[:, b:], bq, bk, bv, gq, gk, 1e-6, positions, cos, sin,
+                                                               D // 2, False, k_pool, v_pool, mapping, H, G, D, DV))
+        out[f"{name}_project_norm_rotate_store"] = rated(us, moved=moved)
+        us = time_kernel(lambda: ops.rotate_norm_store(qkv[:, :a], qkv[:, a:b], qkv[:, b:], positions, cos, sin, D // 2, True, True, 1e-6,
+                                                       vcos, vsin, DV, k_pool, v_pool, mapping, H, G, D, DV))
+        out[f"{name}_rotate_norm_store_kivezen"] = rated(us, moved=moved)
+        # the gated delta rule (convolution, its stored inputs, the walk with norm and gate) beside Kivezen's lightning layer
+        C = 2 * DG * D + DH * DV
+        floats = DH * D * DV
+        state = torch.zeros((sequences + 1, floats + (taps - 1) * C), dtype=torch.float32, device=dev)
+        proj = torch.randn((rows, C + 16 + DH * DV), device=dev).to(bf)
+        conv_w = torch.randn((C, taps), device=dev)
+        decay, dt_bias, gain = -torch.rand(DH, device=dev), torch.randn(DH, device=dev), torch.ones(DV, device=dev)
+        y = torch.empty((rows, DH * DV), dtype=bf, device=dev)
+
+        def delta():
+            conv = ops.short_conv(proj[:, :C], conv_w, state, floats, slots, cu, q_len, activation="silu", store_tail=True)
+            ops.gated_delta_scan(conv, 0, DG * D, 2 * DG * D, proj[:, C:C + DH], proj[:, C + 8:C + 8 + DH], proj[:, C + 16:], decay, dt_bias, gain,
+                                 1e-6, 1e-6, state, 0, slots, cu, DH, DG, D, DV, y)
+
+        us = time_kernel(delta)
+        moved = rows * (C * 2 + C * 8 + 2 * DH * DV * 2) + sequences * floats * 8
+        out[f"{name}_gated_delta_rule"] = dict(rated(us, moved=moved), fp32_tflops=rows * DH * 6 * D * DV / us / 1e6)
+        us = time_kernel(lambda: ops.gated_delta_scan(ops.short_conv(proj[:, :C], conv_w, state, floats, slots, cu, q_len, activation="silu"), 0,
+                                                      DG * D, 2 * DG * D, proj[:, C:C + DH], proj[:, C + 8:C + 8 + DH], proj[:, C + 16:], decay,
+                                                      dt_bias, gain, 1e-6, 1e-6, state, 0, slots, cu, DH, DG, D, DV, y)) - \
+            time_kernel(lambda: ops.short_conv(proj[:, :C], conv_w, state, floats, slots, cu, q_len, activation="silu"))
+        out[f"{name}_gated_delta_rule_walk_alone"] = {"us": us, "fp32_tflops": rows * DH * 6 * D * DV / us / 1e6}
+        lstate = torch.zeros((sequences + 1, DH, D, DV), dtype=torch.float32, device=dev)
+        lproj = torch.randn((rows, 2 * DH * D + 2 * DH * DV), device=dev).to(bf)
+        a, b, c = DH * D, 2 * DH * D, 2 * DH * D + DH * DV
+        raw = torch.empty((rows, DH * DV), dtype=torch.float32, device=dev)
+        ldecay, lgain = torch.full((DH,), 0.99, device=dev), torch.ones(DH * DV, device=dev)
+        us = time_kernel(lambda: (ops.retention_scan(lproj[:, :a], lproj[:, a:b], lproj[:, b:c], None, positions, None, None, 0, ldecay, 1.0, 1e-6,
+                                                     lstate, slots, cu, DH, D, DV, None, 1.0, q_len, input_activation="silu", raw_out=raw),
+                                  ops.group_norm_gate(raw, lgain, lproj[:, c:], y, 1e-6, "sigmoid")))
+        out[f"{name}_lightning_kivezen"] = dict(rated(us, moved=rows * (2 * DH * D + 3 * DH * DV) * 2 + rows * DH * DV * 8 + sequences * floats * 8),
+                                                fp32_tflops=rows * DH * 4 * D * DV / us / 1e6)
+        # the recurrent block (convolution, the gates' small products, the walk) beside Kabanex's minGRU walk of equal width
+        rstate = torch.zeros((sequences + 1, R * taps), dtype=torch.float32, device=dev)
+        rproj = torch.randn((rows, 3 * R), device=dev).to(bf)
+        rconv, gates_w = torch.randn((R, taps), device=dev), torch.randn((B, 2 * (R // B), R // B), device=dev) * 0.05
+        gates_twice = torch.cat([gates_w, gates_w], dim=2).to(bf).contiguous()
+        vec = [torch.randn(R, device=dev) for _ in range(5)]
+        rate = -8.0 * torch.rand(R, device=dev)
+        ry = torch.empty((rows, R), dtype=bf, device=dev)
+
+        def recurrent():
+            sums = torch.empty((rows, 2 * R), dtype=torch.float32, device=dev)
+            if rows > ops.WIDE_ROWS:  # (as the part runs them: a prompt's gate products on the tensor cores, u as two bfloat16 numbers)
+                u, split = ops.short_conv(rproj[:, R:2 * R], rconv, rstate, R, slots, cu, q_len, in_bias=vec[0], out_bias=vec[1],
+                                          store_tail=True, split_per=R // B)
+                for blk in range(B):
+                    at = blk * 2 * (R // B)
+                    ops.gemm_tcgen05(split[:, at:at + 2 * (R // B)], gates_twice[blk], ops.EPI_F32, out=sums[:, at:at + 2 * (R // B)])
+            else:
+                u = ops.short_conv(rproj[:, R:2 * R], rconv, rstate, R, slots, cu, q_len, in_bias=vec[0], out_bias=vec[1], store_tail=True)
+                ops.head_linear(u, gates_w, sums, B, tensor_cores=False)
+            ops.rglru_scan(sums, R // B, u, rproj[:, :R], vec[2], vec[3], vec[4], rate, rstate, 0, slots, cu, q_len, ry)
+
+        us = time_kernel(recurrent)
+        out[f"{name}_recurrent_block"] = dict(rated(us, moved=rows * R * (2 + 4 + 4 + 8 + 8 + 4 + 2 + 2)), gate_products_tflops=rows * 4 * R * (R // B) / us / 1e6)
+        mstate = torch.zeros((sequences + 1, R), dtype=torch.float32, device=dev)
+        us = time_kernel(lambda: ops.mingru_scan(rproj[:, :R], rproj[:, R:2 * R], rproj[:, 2 * R:], vec[0], vec[1], mstate, slots, cu, q_len, ry))
+        out[f"{name}_mingru_walk_kabanex"] = rated(us, moved=rows * R * 8)
+        # routed experts: a scored router with a correction and groups, identity experts, the plain gated form; beside Kivezen's
+        x = torch.randn((rows, W), device=dev).to(bf)
+        router = (torch.randn((E + I, W), device=dev) * 0.02).to(bf)
+        router_k = router[:E].contiguous()
+        correction = torch.randn(E + I, device=dev) * 0.01
+        w_gate_up = (torch.randn((2, E, F, W), device=dev) * 0.02).to(bf)
+        w_gate, w_up = w_gate_up[0], w_gate_up[1]
+        w_down = (torch.randn((E, W, F), device=dev) * 0.02).to(bf)
+        inf = float("inf")
+
+        def routed(scored):
+            if scored:
+                chosen, weights = ops.router_topk(x, router, top, scored=True, correction=correction, groups=z["groups"][0], keep=z["groups"][1],
+                                                  weight_scale=2.5)
+                limit, slope, offset, extra = inf, 1.0, 0.0, dict(chosen=chosen, experts=E, rows=x)
+            else:
+                chosen, weights = ops.router_topk(x, router_k, top)
+                limit, slope, offset, extra = 7.0, 1.702, 1.0, {}
+            if chosen.numel() <= ops.EXPERT_ROWS_ENTRIES:
+                mid = ops.expert_rows_first(x, w_gate, w_up, chosen, limit, slope, offset)
+                return ops.expert_combine(ops.expert_rows_second(mid, w_down, chosen), weights, **extra)
+            if chosen.numel() >= ops.GROUPED_ROWS_PER_EXPERT * E:
+                plan = ops.route_pad(chosen, E)
+                mid = ops.grouped_first_product(ops.gather_rows(x, plan), w_gate_up, plan, limit, slope, offset)
+                return ops.expert_combine(ops.grouped_second_product(mid, w_down, plan), weights, position=plan.position, **extra)
+            plan = ops.route_sort(chosen, E)
+            mid = ops.expert_first_product(x, w_gate, w_up, plan, limit, slope, up_offset=offset)
+            return ops.expert_combine(ops.expert_second_product(mid, w_down, plan), weights, **extra)
+
+        flops = rows * top * 6 * W * F  # (an upper bound for the design: identity experts' entries skip the products)
+        touched = min(E, rows * top)
+        for title, scored in (("routed_experts", True), ("routed_experts_kivezen", False)):
+            us = time_kernel(lambda: routed(scored))
+            out[f"{name}_{title}"] = rated(us, flops=flops) if q_len > 1 else rated(us, moved=touched * 3 * W * F * 2)
+        # the norm on a sublayer's result, the scale, the addition and the copy for the next reader in one kernel; beside the
+        # residual add and RMS norm of a pre-norm layer
+        stream, res, res2 = (torch.randn((rows, W), device=dev) for _ in range(3))
+        ones = torch.ones(W, device=dev)
+        us = time_kernel(lambda: ops.outnorm_add(stream, res, ones, ones, 1e-6, copy_dtype=bf))
+        out[f"{name}_result_norm_add"] = rated(us, moved=rows * W * (4 + 8 + 2))
+        us = time_kernel(lambda: ops.outnorm_add(stream, res, ones, ones, 1e-6, b=res2, gain_a=ones, gain_b=ones, copy_dtype=bf))
+        out[f"{name}_pair_result_norm_add"] = rated(us, moved=rows * W * (8 + 8 + 2))
+        us = time_kernel(lambda: ops.add_rmsnorm(stream, res, ones, 1e-6, bf))
+        out[f"{name}_add_rmsnorm_llama"] = rated(us, moved=rows * W * (4 + 8 + 2))
+    return out
+
+
 def design_run(args) -> int:
     import torch
 
@@ -789,11 +1015,17 @@ def design_run(args) -> int:
         title, all_sizes, make, params, beside, alone = "Kivezen", KIVEZEN_SIZES, kivezen_config, kivezen_layer_params, \
             lovurax_of_equal_size, kivezen_kernels
         other, other_title = "lovurax", "Lovurax of equal size (the parameters a token uses)"
+    elif args.design == "rolevik":
+        title, all_sizes, make, params, beside, alone = "Rolevik", ROLEVIK_SIZES, rolevik_config, rolevik_layer_params, \
+            kivezen_of_equal_size, rolevik_kernels
+        other, other_title = "kivezen", "Kivezen of equal size (the parameters a token uses; one residual stream)"
     else:
         title, all_sizes, make, params, beside, alone = "Lovurax", LOVURAX_SIZES, lovurax_config, lovurax_layer_params, \
             (lambda z: llama_of_equal_size(z, lovurax_layer_params(z))), lovurax_kernels
     sizes = {}
     for name, z in all_sizes.items():
+        if args.size and name != args.size:
+            continue
         entry = {"sizes": z, "layer_params": params(z)}
         for arch, config in ((args.design, make(z)), (other, beside(z))):
             model = make_model(config, batch, prefill_tokens + 64)
@@ -834,8 +1066,9 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the workload's prefill alone and print its figures (for profiling)")
-    parser.add_argument("--design", default=None, choices=["kabanex", "lovurax", "kivezen"],
-                        help="instead of the default run: this design beside a model of equal size (a Llama; for kivezen a Lovurax): "
+    parser.add_argument("--size", default=None, choices=["s", "m"], help="with --design: one of its two sizes alone")
+    parser.add_argument("--design", default=None, choices=["kabanex", "lovurax", "kivezen", "rolevik"],
+                        help="instead of the default run: this design beside a model of equal size (a Llama; for kivezen a Lovurax, for rolevik a Kivezen): "
                              "prefill, decode, its kernels alone")
     args = parser.parse_args()
     if args.design and args.impl == "ours":

@@ -980,11 +980,14 @@ def _state_rows(state: torch.Tensor, offset: int, floats: int, name: str):
 
 def short_conv(x: torch.Tensor, weights: torch.Tensor, state: torch.Tensor, state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor,
                max_q_len: int, in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None,
-               activation: Optional[str] = None) -> torch.Tensor:
+               activation: Optional[str] = None, store_tail: bool = False, split_per: int = 0):
     """A short causal convolution over time per channel: with x_t = x[t] (+ in_bias) and `weights` [channels, taps] whose last
     column meets the current token, out[t] = act(sum_i weights[:, taps - 1 - i] * x_(t - i) (+ out_bias)) as float32
     [tokens, channels].  The inputs before a step's first token come from the sequence's tail, [taps - 1, channels] float32 at
-    `state_offset` floats into its row of `state` (zeros for a new sequence); `short_conv_tail` stores the new tail."""
+    `state_offset` floats into its row of `state` (zeros for a new sequence); with `store_tail` the new tail is stored by the
+    same kernel (else the state is left as it is).  `split_per` n > 0: also returns the results as two bfloat16 numbers
+    each (the rounding and the rest), block by block of n channels, [tokens, channels / n * 2 n] with a block's roundings before
+    its rests: (out, split)."""
     _cuda(x, weights, state, slots, cu_q, in_bias, out_bias)
     _int32(slots, "slots")
     _int32(cu_q, "cu_q")
@@ -999,24 +1002,14 @@ def short_conv(x: torch.Tensor, weights: torch.Tensor, state: torch.Tensor, stat
         raise KernelError(f"short_conv: activation {activation!r} is not built (known: silu or none)")
     tail, stride = _state_rows(state, state_offset, (taps - 1) * channels, "short_conv")
     out = torch.empty((x.shape[0], channels), dtype=torch.float32, device=x.device)
+    if split_per and (split_per < 0 or channels % split_per):
+        raise KernelError(f"short_conv: {channels} channels are no whole blocks of {split_per}")
+    split = torch.empty((x.shape[0], 2 * channels), dtype=torch.bfloat16, device=x.device) if split_per else None
     lib = gated_delta_library()
     _run(lib, lib.mb_short_conv(_p(x), x.stride(0), _code(x.dtype), _p(in_bias), _p(weights), _p(out_bias), CONV_ACTIVATIONS[activation],
                                 _p(out), out.stride(0), tail, stride, _p(slots), _p(cu_q), cu_q.numel() - 1, max_q_len, channels, taps,
-                                _stream()))
-    return out
-
-
-def short_conv_tail(x: torch.Tensor, taps: int, state: torch.Tensor, state_offset: int, slots: torch.Tensor, cu_q: torch.Tensor,
-                    in_bias: Optional[torch.Tensor] = None) -> None:
-    """Stores every sequence's new tail: its last taps - 1 inputs x (+ in_bias), from the step's rows and, where the step brought
-    fewer, from the old tail.  To be called after `short_conv` has read the old one."""
-    _cuda(x, state, slots, cu_q, in_bias)
-    _columns(x, "x")
-    channels = x.shape[1]
-    tail, stride = _state_rows(state, state_offset, (taps - 1) * channels, "short_conv_tail")
-    lib = gated_delta_library()
-    _run(lib, lib.mb_short_conv_tail(_p(x), x.stride(0), _code(x.dtype), _p(in_bias), tail, stride, _p(slots), _p(cu_q),
-                                     cu_q.numel() - 1, channels, taps, _stream()))
+                                1 if store_tail else 0, _p(split), int(split_per), _stream()))
+    return (out, split) if split_per else out
 
 
 def gated_delta_scan(conv: torch.Tensor, q_at: int, k_at: int, v_at: int, a_in: torch.Tensor, b_in: torch.Tensor, gate_in: torch.Tensor,
@@ -1025,7 +1018,7 @@ def gated_delta_scan(conv: torch.Tensor, q_at: int, k_at: int, v_at: int, a_in: 
                      out: torch.Tensor, out_scale: float = 1.0) -> None:
     """The gated delta rule over the new tokens of every sequence.  `conv` float32 [tokens, n] holds the convolved q (kv_heads
     heads of `dim` from column q_at), k (from k_at) and v (heads heads of `vdim` from v_at); q and k become unit vectors
-    x / sqrt(sum x^2 + unit_eps), q times dim^-1/2; beta = sigmoid(b_in), g = exp(decay * softplus(a_in + dt_bias)) per head
+    x / sqrt(sum x^2 + unit_eps), q times dim^-1/2 (in place: `conv` is changed); beta = sigmoid(b_in), g = exp(decay * softplus(a_in + dt_bias)) per head
     (decay = -exp(A_log)); per head, from the sequence's float32 state S [heads, dim, vdim] at `state_offset` floats into its
     row of `state` (updated in place): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = out_scale * o / rms(o)
     * gain * silu(gate_in), rms over the head (eps `eps`).  a_in, b_in [tokens, heads], gate_in and out [tokens, heads * vdim]
@@ -1046,11 +1039,13 @@ def gated_delta_scan(conv: torch.Tensor, q_at: int, k_at: int, v_at: int, a_in: 
         if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
             raise KernelError(f"gated_delta_scan: {name} must be contiguous float32 of {n} elements")
     rows, stride = _state_rows(state, state_offset, heads * dim * vdim, "gated_delta_scan")
+    raw = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=conv.device)  # the read-outs, between the walk and the norm
     lib = gated_delta_library()
     _run(lib, lib.mb_gated_delta_scan(_p(conv), conv.stride(0), _p(a_in), _p(b_in), _p(gate_in), a_in.stride(0), _code(out.dtype), _p(decay),
                                       _p(dt_bias), _p(gain), ctypes.c_float(unit_eps), ctypes.c_float(eps), rows, stride, _p(slots),
-                                      _p(cu_q), cu_q.numel() - 1, _p(out), out.stride(0), ctypes.c_float(out_scale), heads, kv_heads, dim,
-                                      vdim, q_at, k_at, v_at, _stream()))
+                                      _p(cu_q), cu_q.numel() - 1, tokens, _p(raw), _p(out), out.stride(0), ctypes.c_float(out_scale), heads,
+                                      kv_heads, dim, vdim, q_at, k_at, v_at, _stream()))
+    _launches[0] += 2  # three kernels: unit vectors, the walk, norm and gate
 
 
 def rglru_scan(gates: torch.Tensor, per: int, u: torch.Tensor, y_in: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor,

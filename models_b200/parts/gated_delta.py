@@ -79,8 +79,8 @@ class GatedDeltaMixer(SplitPart, Mixer):
         qkv = proj[:, at[0]:at[0] + self.channels]
         a_in, b_in = proj[:, at[1]:at[1] + H], proj[:, at[2]:at[2] + H]
         gate = proj[:, at[3]:at[3] + self.v_width]
-        conv = ops.short_conv(qkv, self.conv, run.state, self.state_floats, batch.slots, batch.cu_q, batch.max_q_len, activation="silu")
-        ops.short_conv_tail(qkv, s.conv_taps, run.state, self.state_floats, batch.slots, batch.cu_q)
+        conv = ops.short_conv(qkv, self.conv, run.state, self.state_floats, batch.slots, batch.cu_q, batch.max_q_len, activation="silu",
+                              store_tail=True)
         ops.gated_delta_scan(conv, 0, self.qk_width, 2 * self.qk_width, a_in, b_in, gate, self.decay, self.dt_bias, self.gain,
                              s.unit_eps, s.eps, run.state, 0, batch.slots, batch.cu_q, H, s.num_kv_heads, s.head_dim, s.value_dim,
                              mid, scale)

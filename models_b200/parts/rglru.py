@@ -52,6 +52,12 @@ class RglruMixer(SplitPart, Mixer):
         self.conv, self.conv_bias = rt.vector(tensors[n["conv"]]), rt.vector(tensors[n["conv_bias"]])
         # both gates' matrices of a block one below the other: one small product per block gives [r sums | i sums]
         self.gates = torch.cat([rt.vector(tensors[n["gate_a"]]), rt.vector(tensors[n["gate_i"]])], dim=1).contiguous()
+        # for prompts in the bfloat16 mode: every block's matrices twice side by side, [2 per, 2 per] bfloat16 (see `inner`)
+        self.gates_twice = None
+        if rt.mode == "bfloat16" and tensors[n["gate_a"]].dtype == torch.bfloat16 and tensors[n["gate_i"]].dtype == torch.bfloat16:
+            twice = torch.cat([self.gates, self.gates], dim=2).to(torch.bfloat16).contiguous()
+            if twice.is_cuda and ops.gemm_tcgen05_takes(twice[0], ops.EPI_F32) and (2 * self.per) % 8 == 0:
+                self.gates_twice = twice
         self.r_bias = rt.vector(tensors[n["gate_a_bias"]]).reshape(-1).contiguous()
         self.i_bias = rt.vector(tensors[n["gate_i_bias"]]).reshape(-1).contiguous()
         self.rate = (-float(s.rate) * torch.nn.functional.softplus(rt.vector(tensors[n["lam"]]))).contiguous()  # log a = rate * r
@@ -71,10 +77,20 @@ class RglruMixer(SplitPart, Mixer):
             raise RuntimeError("the recurrent block needs its per-sequence state; its run has none")
         R, at = s.width, self.starts
         y_in, x_in = proj[:, at[0]:at[0] + R], proj[:, at[1]:at[1] + R]
-        u = ops.short_conv(x_in, self.conv, run.state, R, batch.slots, batch.cu_q, batch.max_q_len, in_bias=self.x_bias, out_bias=self.conv_bias)
-        ops.short_conv_tail(x_in, s.conv_taps, run.state, R, batch.slots, batch.cu_q, in_bias=self.x_bias)
-        sums = torch.empty((u.shape[0], 2 * R), dtype=torch.float32, device=u.device)
-        ops.head_linear(u, self.gates, sums, s.blocks, tensor_cores=False)
+        rows = proj.shape[0]
+        sums = torch.empty((rows, 2 * R), dtype=torch.float32, device=proj.device)
+        if self.gates_twice is not None and rows > ops.WIDE_ROWS:
+            # a prompt: the gates' small products on the tensor cores.  u goes in as two bfloat16 numbers (its rounding and the
+            # rest, side by side along K, against the block's matrices repeated), so the sums keep float accuracy
+            u, split = ops.short_conv(x_in, self.conv, run.state, R, batch.slots, batch.cu_q, batch.max_q_len, in_bias=self.x_bias,
+                                      out_bias=self.conv_bias, store_tail=True, split_per=self.per)
+            for b in range(s.blocks):
+                at = b * 2 * self.per
+                ops.gemm_tcgen05(split[:, at:at + 2 * self.per], self.gates_twice[b], ops.EPI_F32, out=sums[:, at:at + 2 * self.per])
+        else:
+            u = ops.short_conv(x_in, self.conv, run.state, R, batch.slots, batch.cu_q, batch.max_q_len, in_bias=self.x_bias,
+                               out_bias=self.conv_bias, store_tail=True)
+            ops.head_linear(u, self.gates, sums, s.blocks, tensor_cores=False)
         ops.rglru_scan(sums, self.per, u, y_in, self.r_bias, self.i_bias, self.y_bias, self.rate, run.state, 0, batch.slots, batch.cu_q,
                        batch.max_q_len, mid, scale)
 
