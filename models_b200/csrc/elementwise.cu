@@ -422,6 +422,81 @@ __global__ void outnorm_add_kernel(float* __restrict__ x, const float* __restric
     }
 }
 
+// The same for rows of up to 8 elements a thread: everything a thread needs is asked for at once and kept in registers, so
+// the row's trips to memory overlap instead of following one another (a decode step's handful of rows is all latency).
+// Two sums meet in one round of the block.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* scratch /* >= 32 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = make_float2(a, b);
+    __syncthreads();
+    const float2 mine = lane < warps ? scratch[lane] : make_float2(0.0f, 0.0f);
+    return make_float2(warp_sum(mine.x), warp_sum(mine.y));
+}
+
+template <typename Out>
+__global__ void outnorm_add_registers_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                                             const float* __restrict__ gain_a, const float* __restrict__ gain_b,
+                                             const float* __restrict__ weight, const float* __restrict__ scale, Out* __restrict__ copy,
+                                             int width, float eps) {
+    grid_launch_dependents();
+    constexpr int kPer = 8;
+    __shared__ float2 scratch[32];
+    const size_t at = (size_t)blockIdx.x * width;
+    float vw[kPer], vs[kPer], vga[kPer], vgb[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {  // (what no kernel of the step writes may be asked for before the kernels before this one are done)
+        const int i = threadIdx.x + j * blockDim.x;
+        const bool in = i < width;
+        vw[j] = in ? weight[i] : 0.0f;
+        vs[j] = in ? scale[i] : 0.0f;
+        vga[j] = (in && b != nullptr) ? gain_a[i] : 0.0f;
+        vgb[j] = (in && b != nullptr) ? gain_b[i] : 0.0f;
+    }
+    grid_dependency_wait();
+    float va[kPer], vb[kPer], vx[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const bool in = i < width;
+        va[j] = in ? a[at + i] : 0.0f;
+        vb[j] = (in && b != nullptr) ? b[at + i] : 0.0f;
+        vx[j] = in ? x[at + i] : 0.0f;
+    }
+    float y[kPer], sum = 0.0f;
+    if (b != nullptr) {
+        float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) sa = fmaf(va[j], va[j], sa), sb = fmaf(vb[j], vb[j], sb);
+        const float2 both = block_sum2(sa, sb, scratch);
+        const float ia = 1.0f / sqrtf(both.x / (float)width + eps), ib = 1.0f / sqrtf(both.y / (float)width + eps);
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) sum += (y[j] = 0.5f * (va[j] * ia * vga[j] + vb[j] * ib * vgb[j]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) sum += (y[j] = va[j]);
+    }
+    const float mean = block_sum2(sum, 0.0f, scratch).x / (float)width;
+    float squares = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const float d = threadIdx.x + j * blockDim.x < width ? y[j] - mean : 0.0f;
+        squares = fmaf(d, d, squares);
+    }
+    const float inv = 1.0f / sqrtf(block_sum2(squares, 0.0f, scratch).x / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < width) {
+            const float v = vx[j] + vs[j] * ((y[j] - mean) * inv * vw[j]);
+            x[at + i] = v;
+            if (copy != nullptr) Num<Out>::store(copy + at + i, v);
+        }
+    }
+}
+
 // dst = src in another storage type, element by element.
 template <typename Out>
 __global__ void store_rows_kernel(const float* __restrict__ src, Out* __restrict__ dst, size_t total) {
@@ -670,6 +745,19 @@ MB_EXPORT int mb_outnorm_add(float* x, const float* a, const float* b, const flo
     if (rows <= 0 || width <= 0) return 0;
     if (width > 12000) return fail("outnorm_add: rows of %d floats exceed the 12000 a block keeps", width);
     if (b != nullptr && (gain_a == nullptr || gain_b == nullptr)) return fail("outnorm_add: two results need two gains");
+    if (weight != nullptr && width <= 8 * 512 && rows <= 256) {
+        // few rows (decode steps, short portions): a row in its block's registers; as many threads as give every thread 8 elements
+        const int few = ((width + 7) / 8 + 31) / 32 * 32;
+        if (copy == nullptr || copy_dtype == MB_F32)
+            MB_LAUNCH("elementwise", outnorm_add_registers_kernel<float>, dim3(rows), dim3(few), 0, stream, true, x, a, b, gain_a, gain_b,
+                      weight, scale, (float*)copy, width, eps);
+        else if (copy_dtype == MB_BF16)
+            MB_LAUNCH("elementwise", outnorm_add_registers_kernel<__nv_bfloat16>, dim3(rows), dim3(few), 0, stream, true, x, a, b, gain_a,
+                      gain_b, weight, scale, (__nv_bfloat16*)copy, width, eps);
+        else
+            return fail("outnorm_add: unknown dtype code %d", copy_dtype);
+        return check_launch("outnorm_add");
+    }
     const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
     const size_t smem = sizeof(float) * (size_t)width;
     if (copy == nullptr || copy_dtype == MB_F32)

@@ -232,8 +232,10 @@ gated_delta_walk_kernel(const float* __restrict__ conv, int conv_stride, const T
         float seen = 0.0f, o_before = 0.0f;
 #pragma unroll
         for (int i = 0; i < kPer; ++i) seen = fmaf(s[i], k[i], seen);
-        for (int u = 0; u < n; ++u) {
-            take(min(u + 1, n - 1), k_ahead, q_ahead, v_ahead, beta_ahead, g_ahead);
+#pragma unroll  // (all of a group's tokens spelled out: the rows' places in shared memory are constants and no register is copied)
+        for (int u = 0; u < kGroup; ++u) {
+            if (u >= n) break;
+            take(u + 1 < kGroup ? u + 1 : u, k_ahead, q_ahead, v_ahead, beta_ahead, g_ahead);  // (a row beyond the group's tokens holds finite leftovers)
             float decayed[kPer];
 #pragma unroll
             for (int i = 0; i < kPer; ++i) decayed[i] = g * s[i];
