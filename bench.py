@@ -803,7 +803,7 @@ def rolevik_config(z):
     }
     mlps = {"dense": {"kind": "dense", "ff": z["ff"]},
             "moe": {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
-                    "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.5,
+                    "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.0,
                                "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}}
     layers = []
     for i in range(z["layers"]):
@@ -968,7 +968,7 @@ def rolevik_kernels(z, peak, prompt=2048, batch=8, context=1536):
         def routed(scored):
             if scored:
                 chosen, weights = ops.router_topk(x, router, top, scored=True, correction=correction, groups=z["groups"][0], keep=z["groups"][1],
-                                                  weight_scale=2.5)
+                                                  weight_scale=2.0)
                 limit, slope, offset, extra = inf, 1.0, 0.0, dict(chosen=chosen, experts=E, rows=x)
             else:
                 chosen, weights = ops.router_topk(x, router_k, top)
