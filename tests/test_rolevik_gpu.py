@@ -583,6 +583,53 @@ def test_models_of_one_kind_of_layer(cuda_device, tmp_path, kind, dtype):
     engine.cache.check()
 
 
+RLV_MID = model(1000, 384, 1e-6, 0.8, 0.6, [
+    parallel((6, 3, 48, 80, 0.144, 96, (24, 30000.0)), (4, 2, 48, 80, 3), moe(24, 8, 5, 1.8, (8, 3), 96, 160)),
+    rglru(200, 5, 3, dense(640)),
+    parallel((5, 1, 40, 24, 0.16, 250, (40, 1000.0)), (6, 6, 24, 40, 4), dense(512)),
+    rglru(384, 3, 4, moe(10, 0, 2, 1.0, (2, 1), 128)),
+])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_mid_sized_model_long_prompts_and_batches(cuda_device, tmp_path, dtype):
+    """Sizes between the small configurations and the benchmark's (heads of 48 and 40, values of 80 and 24, 32 router outputs in
+    8 groups, chunks of 96 and 250): a prompt of 700 tokens whole, then decoded across chunk edges; three unequal prompts in one
+    step (1, 300 and 650 tokens), then decoded together while the short one ends."""
+    from models_b200.engine import StepEntry
+
+    folder = make_folder(RLV_MID, 77, tmp_path, std=0.08)
+    engine = _engine(folder, dtype, max_tokens=4096)
+    vocab = RLV_MID["vocab"]
+    tokens = random_tokens(vocab, 740, 5)
+    expected = plain_logits(folder, tokens)
+    want_rows = [0, 95, 96, 97, 249, 250, 251, 383, 384, 500, 699]
+    slot = engine.open_slot()
+    rows = [engine.step([StepEntry(slot, tokens[:700], want_rows)])]
+    for i in range(700, 740):
+        rows.append(engine.step([StepEntry(slot, [tokens[i]], [0])]))
+    assert _close(torch.cat(rows), torch.cat([expected[want_rows], expected[700:]]), dtype)
+    engine.release_slot(slot)
+    lengths, prompts = [9, 330, 680], [1, 300, 650]
+    full = [random_tokens(vocab, n, 30 + i) for i, n in enumerate(lengths)]
+    wanted = [plain_logits(folder, t) for t in full]
+    slots = [engine.open_slot() for _ in full]
+    out = engine.step([StepEntry(s, t[:p], [p - 1]) for s, t, p in zip(slots, full, prompts)])
+    got, want = [out], [torch.stack([wanted[i][p - 1] for i, p in enumerate(prompts)])]
+    live, at = [0, 1, 2], list(prompts)
+    while live:
+        out = engine.step([StepEntry(slots[i], [full[i][at[i]]], [0]) for i in live])
+        got.append(out.clone())
+        want.append(torch.stack([wanted[i][at[i]] for i in live]))
+        for i in list(live):
+            at[i] += 1
+            if at[i] == len(full[i]):
+                engine.release_slot(slots[i])
+                live.remove(i)
+    assert _close(torch.cat(got), torch.cat(want), dtype)
+    engine.cache.check()
+
+
 def test_logits_do_not_depend_on_the_batch_or_the_cut(cuda_device, folders):
     """float32: the same position through a whole prompt, through portions, and inside a batch differs by rounding only."""
     from models_b200.engine import StepEntry
